@@ -13,7 +13,7 @@ import numpy as np
 import torch
 
 
-def embed_gather(table, ids, token_seq, seq_slot, last_token, x_out, status):
+def embed_gather(table, ids, token_seq, seq_slot, last_token, x_out, status, scale=1.0):
     n = x_out.shape[0]
     for t in range(n):
         s = int(token_seq[t])
@@ -27,7 +27,7 @@ def embed_gather(table, ids, token_seq, seq_slot, last_token, x_out, status):
             status |= 1
             x_out[t] = 0
         else:
-            x_out[t] = table[i].float()
+            x_out[t] = table[i].float() * scale
 
 
 def add_rmsnorm(x, delta, weight, eps, out):

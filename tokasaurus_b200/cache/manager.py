@@ -33,10 +33,10 @@ class CacheGroup:
     need: PagedCacheNeed
     entries: list[int]
     allocator: PageAllocator
-    storage: torch.Tensor | None = None  # [len(entries), 2, pages, kv heads, page_size, head_dim]
+    storage: torch.Tensor | None = None  # [len(entries), planes, pages, kv heads, page_size, head_dim]
 
     def bytes_per_token(self, element_size: int) -> int:
-        return 2 * len(self.entries) * self.need.n_kv_heads * self.need.head_dim * element_size
+        return self.need.planes * len(self.entries) * self.need.n_kv_heads * self.need.head_dim * element_size
 
 
 @dataclass
@@ -125,7 +125,7 @@ class CacheManager:
         if self.device is not None:
             for g in self.groups:
                 n = g.need
-                g.storage = torch.zeros((len(g.entries), 2, g.allocator.num_pages, n.n_kv_heads, page_size, n.head_dim),
+                g.storage = torch.zeros((len(g.entries), n.planes, g.allocator.num_pages, n.n_kv_heads, page_size, n.head_dim),
                                         dtype=dtype, device=self.device)
             for entry, need in self._state_need.items():
                 self._state[entry] = torch.zeros((max_requests, *need.shape), dtype=_DTYPES[need.dtype],
@@ -231,7 +231,8 @@ class CacheManager:
         if entry in self._entry_group:
             g, i = self._entry_group[entry]
             st = self.groups[g].storage
-            return PagedLayerCache(g, st[i, 0] if st is not None else None, st[i, 1] if st is not None else None,
+            return PagedLayerCache(g, st[i, 0] if st is not None else None,
+                                   st[i, 1] if st is not None and st.shape[1] > 1 else None,
                                    self.page_size, writable)
         if entry in self._state_need:
             return StateLayerCache(self._state.get(entry), writable)

@@ -64,14 +64,17 @@ def known_architectures() -> list[str]:
 def lookup_architecture(config_dict: dict[str, Any]) -> Architecture:
     """Find the architecture that a config.json dictionary names."""
     _ensure_builtin()
-    for name in config_dict.get("architectures") or ():
+    names = list(config_dict.get("architectures") or ())
+    if isinstance(config_dict.get("architecture"), str):  # some families name one architecture under this key
+        names.append(config_dict["architecture"])
+    for name in names:
         if name in _BY_NAME:
             return _BY_NAME[name]
     mt = config_dict.get("model_type")
     if mt in _BY_MODEL_TYPE:
         return _BY_MODEL_TYPE[mt]
     raise UnknownArchitectureError(
-        f"config.json names architectures={config_dict.get('architectures')!r}, "
+        f"config.json names architectures={names!r}, "
         f"model_type={mt!r}; known architectures: {sorted(_BY_NAME)}"
     )
 
@@ -83,4 +86,4 @@ def _ensure_builtin() -> None:
     global _builtin_loaded
     if not _builtin_loaded:
         _builtin_loaded = True
-        from tokasaurus_b200.models import llama  # noqa: F401  (registers itself)
+        from tokasaurus_b200.models import llama, sozurax  # noqa: F401  (they register themselves)

@@ -8,12 +8,12 @@ using namespace tkb;
 // ------------------------------------------------------------------------------------------------
 // Embedding gather into the float32 residual stream.
 // A token id < 0 means "the token this request sampled last": it is read from last_token[slot].
-// Rows whose token_seq is < 0 are padding and become zero.
+// Rows whose token_seq is < 0 are padding and become zero.  `scale` multiplies the row in float32 (1 for none).
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
                                     const int* __restrict__ last_token, float* __restrict__ x, int H, int V,
-                                    int* __restrict__ status) {
+                                    float scale, int* __restrict__ status) {
   trigger_dependents();
   grid_dependency_wait();
   const int t = blockIdx.x;
@@ -31,29 +31,29 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
     return;
   }
   const T* row = table + (size_t)id * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) xr[i] = to_float(row[i]);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) xr[i] = to_float(row[i]) * scale;
 }
 
 template <typename T>
 static int embed_gather_launch(const void* table, const int* ids, const int* token_seq, const int* seq_slot,
-                               const int* last_token, float* x, int n_tokens, int H, int V, int* status,
-                               cudaStream_t st) {
+                               const int* last_token, float* x, int n_tokens, int H, int V, float scale,
+                               int* status, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
   int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
   return launch_pdl(embed_gather_kernel<T>, dim3(n_tokens), dim3(threads), 0, st, (const T*)table, ids, token_seq, seq_slot,
-                    last_token, x, H, V, status);
+                    last_token, x, H, V, scale, status);
 }
 TKB_EXPORT int tkb_embed_gather_f32(const void* table, const int* ids, const int* token_seq, const int* seq_slot,
-                                    const int* last_token, float* x, int n_tokens, int H, int V, int* status,
-                                    void* st) {
-  return embed_gather_launch<float>(table, ids, token_seq, seq_slot, last_token, x, n_tokens, H, V, status,
+                                    const int* last_token, float* x, int n_tokens, int H, int V, float scale,
+                                    int* status, void* st) {
+  return embed_gather_launch<float>(table, ids, token_seq, seq_slot, last_token, x, n_tokens, H, V, scale, status,
                                     (cudaStream_t)st);
 }
 TKB_EXPORT int tkb_embed_gather_bf16(const void* table, const int* ids, const int* token_seq, const int* seq_slot,
-                                     const int* last_token, float* x, int n_tokens, int H, int V, int* status,
-                                     void* st) {
-  return embed_gather_launch<__nv_bfloat16>(table, ids, token_seq, seq_slot, last_token, x, n_tokens, H, V, status,
-                                            (cudaStream_t)st);
+                                     const int* last_token, float* x, int n_tokens, int H, int V, float scale,
+                                     int* status, void* st) {
+  return embed_gather_launch<__nv_bfloat16>(table, ids, token_seq, seq_slot, last_token, x, n_tokens, H, V, scale,
+                                            status, (cudaStream_t)st);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -1,0 +1,294 @@
+// Attention over a cache of per-token latents ("latent attention"): every token leaves one row
+// [c (rank) | rotated shared key part (rot)] in its request's pages, and all query heads read the same rows.
+// With the key up-projection folded into the query (q_abs = W_uk^T q_plain, done by the caller as a matrix
+// product), a head's score for a key row is  (q_abs . c + q_rot . k_rot) * scale,  and its output in latent
+// space is the softmax-weighted sum of the rows' c, which the caller takes through the value up-projection.
+//
+// Kernels: the preparation of a step's tokens (RMS norms of the query latent and of c, interleaved rotation of the
+// shared key part, write into the pages); the interleaved rotation of the queries' rotated part; the attention
+// itself on the FP32 pipes for any mix of prompt portions and single tokens (scores, softmax weights and sums
+// float32).  Each is built for float and bfloat16 activations.
+//
+// Compile with -DTKB_LAT_RANK=<rank of the latent>.
+#include "common.cuh"
+#include <float.h>
+
+#ifndef TKB_LAT_RANK
+#error "compile with -DTKB_LAT_RANK=<rank of the cached latent>"
+#endif
+
+using namespace tkb;
+
+namespace {
+
+constexpr int RANK = TKB_LAT_RANK;
+constexpr int WARPS = 4;
+constexpr int DPL = (RANK + 31) / 32;  // output elements per lane
+
+// ------------------------------------------------------------------------------------------------
+// One block a token.  proj: float32 [tokens, stride] holding the query latent at column q_off (q_rank wide, absent
+// if q_rank == 0) and the key/value latent at column kv_off (RANK + rot wide, absent if kv_off < 0).
+//   cq = rms(proj[q_off : q_off + q_rank]) * q_w                          -> cq_out [tokens, q_rank]
+//   c  = rms(proj[kv_off : kv_off + RANK]) * kv_w                         -> cache row [0, RANK)
+//   kr = rotate(proj[kv_off + RANK : + rot], position)                    -> cache row [RANK, RANK + rot)
+// The rotation turns the pairs (2i, 2i+1), i < rot_dims / 2, by position * inv_freq[i]; the rest passes.
+template <typename T>
+__global__ void latent_prep_kernel(const float* __restrict__ proj, int stride, int q_off, int q_rank,
+                                   const float* __restrict__ q_w, T* __restrict__ cq_out, int kv_off, int rot,
+                                   int rot_dims, const float* __restrict__ kv_w, const float* __restrict__ inv_freq,
+                                   T* __restrict__ cache, const int* __restrict__ positions,
+                                   const int* __restrict__ token_seq, const int* __restrict__ page_indptr,
+                                   const int* __restrict__ page_ids, int page_size, int num_pages, float eps,
+                                   int* __restrict__ status) {
+  __shared__ float scratch[33];
+  trigger_dependents();
+  grid_dependency_wait();
+  const int t = blockIdx.x;
+  const int s = token_seq[t];
+  if (s < 0) return;
+  const float* row = proj + (size_t)t * stride;
+  if (q_rank > 0) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) ss += row[q_off + i] * row[q_off + i];
+    const float r = rsqrtf(block_sum(ss, scratch) / (float)q_rank + eps);
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
+      cq_out[(size_t)t * q_rank + i] = from_float<T>(row[q_off + i] * r * q_w[i]);
+  }
+  if (kv_off < 0) return;
+  const int p = positions[t];
+  const int page = checked_page(page_ids[page_indptr[s] + p / page_size], num_pages, status);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < RANK; i += blockDim.x) ss += row[kv_off + i] * row[kv_off + i];
+  const float r = rsqrtf(block_sum(ss, scratch) / (float)RANK + eps);
+  if (page < 0) {
+    if (threadIdx.x == 0) atomicOr(status, TKB_STATUS_BAD_PAGE);
+    return;
+  }
+  T* dst = cache + ((size_t)page * page_size + (p % page_size)) * (RANK + rot);
+  for (int i = threadIdx.x; i < RANK; i += blockDim.x) dst[i] = from_float<T>(row[kv_off + i] * r * kv_w[i]);
+  const float* kr = row + kv_off + RANK;
+  for (int i = threadIdx.x; i < rot_dims / 2; i += blockDim.x) {
+    float sn, cs;
+    sincosf((float)p * inv_freq[i], &sn, &cs);
+    const float u = kr[2 * i], v = kr[2 * i + 1];
+    dst[RANK + 2 * i] = from_float<T>(u * cs - v * sn);
+    dst[RANK + 2 * i + 1] = from_float<T>(v * cs + u * sn);
+  }
+  for (int i = rot_dims + threadIdx.x; i < rot; i += blockDim.x) dst[RANK + i] = from_float<T>(kr[i]);
+}
+
+// In place: the pairs (2i, 2i+1), i < rot_dims / 2, of x[t][head][off ...] are turned by position * inv_freq[i].
+template <typename T>
+__global__ void rotate_pairs_kernel(T* __restrict__ x, int token_stride, int head_stride, int off, int n_heads,
+                                    int rot_dims, const float* __restrict__ inv_freq,
+                                    const int* __restrict__ positions, const int* __restrict__ token_seq) {
+  trigger_dependents();
+  grid_dependency_wait();
+  const int t = blockIdx.x;
+  if (token_seq[t] < 0) return;
+  const float p = (float)positions[t];
+  const int half = rot_dims / 2;
+  for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
+    const int h = idx / half, i = idx - h * half;
+    T* q = x + (size_t)t * token_stride + (size_t)h * head_stride + off;
+    float sn, cs;
+    sincosf(p * inv_freq[i], &sn, &cs);
+    const float u = to_float(q[2 * i]), v = to_float(q[2 * i + 1]);
+    q[2 * i] = from_float<T>(u * cs - v * sn);
+    q[2 * i + 1] = from_float<T>(v * cs + u * sn);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float dot_span(const T* __restrict__ k, const float* __restrict__ q, int n, bool vec);
+
+template <>
+__device__ __forceinline__ float dot_span<float>(const float* __restrict__ k, const float* __restrict__ q, int n,
+                                                 bool vec) {
+  float acc = 0.f;
+  if (vec) {
+    const float4* k4 = reinterpret_cast<const float4*>(k);
+    for (int i = 0; i < n / 4; i++) {
+      const float4 v = k4[i];
+      acc = fmaf(v.x, q[4 * i + 0], acc);
+      acc = fmaf(v.y, q[4 * i + 1], acc);
+      acc = fmaf(v.z, q[4 * i + 2], acc);
+      acc = fmaf(v.w, q[4 * i + 3], acc);
+    }
+    return acc;
+  }
+  for (int i = 0; i < n; i++) acc = fmaf(k[i], q[i], acc);
+  return acc;
+}
+template <>
+__device__ __forceinline__ float dot_span<__nv_bfloat16>(const __nv_bfloat16* __restrict__ k,
+                                                         const float* __restrict__ q, int n, bool vec) {
+  float acc = 0.f;
+  if (vec) {
+    const uint4* k8 = reinterpret_cast<const uint4*>(k);
+    for (int i = 0; i < n / 8; i++) {
+      const uint4 v = k8[i];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const float2 f = __bfloat1622float2(h[u]);
+        acc = fmaf(f.x, q[8 * i + 2 * u + 0], acc);
+        acc = fmaf(f.y, q[8 * i + 2 * u + 1], acc);
+      }
+    }
+    return acc;
+  }
+  for (int i = 0; i < n; i++) acc = fmaf(__bfloat162float(k[i]), q[i], acc);
+  return acc;
+}
+
+// One warp owns one (token, head).  A token at position p sees the rows of positions max(0, p - window + 1) .. p of
+// its own request (window <= 0: all); the step's own rows are in the cache already.  Lane j scores row base + j;
+// after the warp-wide running maximum and sum are brought up to date, lane d accumulates latent elements d, d + 32, ...
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32)
+latent_attn_simt_kernel(const T* __restrict__ q_abs, long long qa_token_stride, long long qa_head_stride,
+                        const T* __restrict__ q_rot, long long qr_token_stride, long long qr_head_stride, int rot,
+                        T* __restrict__ out, const T* __restrict__ cache, const int* __restrict__ token_seq,
+                        const int* __restrict__ positions, const int* __restrict__ page_indptr,
+                        const int* __restrict__ page_ids, const int* __restrict__ rows, int n_heads, int page_size,
+                        float scale_log2, int window, int num_pages, int* __restrict__ status) {
+  extern __shared__ float qs_all[];  // [WARPS][RANK + rot]
+  trigger_dependents();
+  grid_dependency_wait();
+  const int t = rows ? rows[blockIdx.x] : blockIdx.x;
+  const int s = token_seq[t];
+  if (s < 0) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int h = blockIdx.y * WARPS + warp;
+  if (h >= n_heads) return;
+  const int width = RANK + rot;
+  float* qs = qs_all + (size_t)warp * width;
+  const int p = positions[t];
+  const int* table = page_ids + page_indptr[s];
+  int lo = 0;
+  if (window > 0 && p - window + 1 > 0) lo = p - window + 1;
+  const T* qa = q_abs + (size_t)t * qa_token_stride + (size_t)h * qa_head_stride;
+  const T* qr = q_rot + (size_t)t * qr_token_stride + (size_t)h * qr_head_stride;
+  for (int d = lane; d < RANK; d += 32) qs[d] = to_float(qa[d]) * scale_log2;
+  for (int d = lane; d < rot; d += 32) qs[RANK + d] = to_float(qr[d]) * scale_log2;
+  __syncwarp();
+  const bool vec = (width * sizeof(T)) % 16 == 0;
+
+  float m = -FLT_MAX, l = 0.f;
+  float acc[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; i++) acc[i] = 0.f;
+  for (int base = lo; base <= p; base += 32) {
+    const int j = base + lane;
+    const bool live = j <= p;
+    long long rowoff = 0;
+    float sc = -FLT_MAX;
+    if (live) {
+      const int page = checked_page(table[j / page_size], num_pages, status);
+      if (page >= 0) {
+        rowoff = ((long long)page * page_size + (j % page_size)) * width;
+        sc = dot_span<T>(cache + rowoff, qs, width, vec);
+      }
+    }
+    const float m_new = fmaxf(m, warp_max(sc));
+    const float alpha = exp2f(m - m_new);
+    const float pj = (live && sc > -FLT_MAX) ? exp2f(sc - m_new) : 0.f;
+    l = l * alpha + warp_sum(pj);
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < DPL; i++) acc[i] *= alpha;
+    const int nlive = (p - base + 1) < 32 ? (p - base + 1) : 32;
+    for (int jj = 0; jj < nlive; jj++) {
+      const float pv = __shfl_sync(0xffffffffu, pj, jj);
+      const long long ro = __shfl_sync(0xffffffffu, rowoff, jj);
+      const T* crow = cache + ro;
+#pragma unroll
+      for (int i = 0; i < DPL; i++) {
+        const int d = lane + 32 * i;
+        if (d < RANK) acc[i] = fmaf(pv, to_float(crow[d]), acc[i]);
+      }
+    }
+  }
+  const float inv_l = l > 0.f ? 1.f / l : 0.f;
+  T* orow = out + ((size_t)blockIdx.x * n_heads + h) * RANK;
+#pragma unroll
+  for (int i = 0; i < DPL; i++) {
+    const int d = lane + 32 * i;
+    if (d < RANK) orow[d] = from_float<T>(acc[i] * inv_l);
+  }
+}
+
+template <typename T>
+int prep_launch(const float* proj, int stride, int q_off, int q_rank, const float* q_w, void* cq_out, int kv_off,
+                int rot, int rot_dims, const float* kv_w, const float* inv_freq, void* cache, const int* positions,
+                const int* token_seq, const int* page_indptr, const int* page_ids, int page_size, int num_pages,
+                float eps, int n_tokens, int* status, cudaStream_t st) {
+  if (n_tokens <= 0) return 0;
+  if (rot_dims < 0 || rot_dims > rot || rot_dims % 2 || page_size <= 0) return -2;
+  return launch_pdl(latent_prep_kernel<T>, dim3(n_tokens), dim3(128), 0, st, proj, stride, q_off, q_rank, q_w,
+                    (T*)cq_out, kv_off, rot, rot_dims, kv_w, inv_freq, (T*)cache, positions, token_seq, page_indptr,
+                    page_ids, page_size, num_pages, eps, status);
+}
+
+template <typename T>
+int rotate_launch(void* x, int token_stride, int head_stride, int off, int n_heads, int rot_dims,
+                  const float* inv_freq, const int* positions, const int* token_seq, int n_tokens, cudaStream_t st) {
+  if (n_tokens <= 0 || rot_dims <= 0) return 0;
+  if (rot_dims % 2) return -2;
+  return launch_pdl(rotate_pairs_kernel<T>, dim3(n_tokens), dim3(128), 0, st, (T*)x, token_stride, head_stride, off,
+                    n_heads, rot_dims, inv_freq, positions, token_seq);
+}
+
+template <typename T>
+int attn_launch(const void* q_abs, long long qa_ts, long long qa_hs, const void* q_rot, long long qr_ts, long long qr_hs,
+                int rot, void* out, const void* cache, const int* token_seq, const int* positions,
+                const int* page_indptr, const int* page_ids, const int* rows, int n_rows, int n_heads, int page_size,
+                float scale, int window, int num_pages, int* status, cudaStream_t st) {
+  if (n_rows <= 0) return 0;
+  if (n_heads <= 0 || page_size <= 0 || rot < 0) return -2;
+  const int hb = (n_heads + WARPS - 1) / WARPS;
+  if (hb > 65535) return -3;
+  const size_t smem = (size_t)WARPS * (RANK + rot) * sizeof(float);
+  if (smem > 200 * 1024) return -2;
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(latent_attn_simt_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return launch_pdl(latent_attn_simt_kernel<T>, dim3(n_rows, hb), dim3(WARPS * 32), smem, st, (const T*)q_abs, qa_ts,
+                    qa_hs, (const T*)q_rot, qr_ts, qr_hs, rot, (T*)out, (const T*)cache, token_seq, positions,
+                    page_indptr, page_ids, rows, n_heads, page_size, scale * 1.4426950408889634f, window, num_pages,
+                    status);
+}
+
+}  // namespace
+
+#define TKB_LATENT_EXPORTS(SUF, T)                                                                                     \
+  TKB_EXPORT int tkb_latent_prep_##SUF(const float* proj, int stride, int q_off, int q_rank, const float* q_w,         \
+                                       void* cq_out, int kv_off, int rot, int rot_dims, const float* kv_w,             \
+                                       const float* inv_freq, void* cache, const int* positions, const int* token_seq, \
+                                       const int* page_indptr, const int* page_ids, int page_size, int num_pages,      \
+                                       float eps, int n_tokens, int* status, void* st) {                               \
+    return prep_launch<T>(proj, stride, q_off, q_rank, q_w, cq_out, kv_off, rot, rot_dims, kv_w, inv_freq, cache,      \
+                          positions, token_seq, page_indptr, page_ids, page_size, num_pages, eps, n_tokens, status,    \
+                          (cudaStream_t)st);                                                                           \
+  }                                                                                                                    \
+  TKB_EXPORT int tkb_rotate_pairs_##SUF(void* x, int token_stride, int head_stride, int off, int n_heads,              \
+                                        int rot_dims, const float* inv_freq, const int* positions,                     \
+                                        const int* token_seq, int n_tokens, void* st) {                                \
+    return rotate_launch<T>(x, token_stride, head_stride, off, n_heads, rot_dims, inv_freq, positions, token_seq,      \
+                            n_tokens, (cudaStream_t)st);                                                               \
+  }                                                                                                                    \
+  TKB_EXPORT int tkb_latent_attn_simt_##SUF(const void* q_abs, long long qa_ts, long long qa_hs, const void* q_rot,    \
+                                            long long qr_ts, long long qr_hs, int rot, void* out, const void* cache,   \
+                                            const int* token_seq, const int* positions, const int* page_indptr,        \
+                                            const int* page_ids, const int* rows, int n_rows, int n_heads,             \
+                                            int page_size, float scale, int window, int num_pages, int* status,        \
+                                            void* st) {                                                                \
+    return attn_launch<T>(q_abs, qa_ts, qa_hs, q_rot, qr_ts, qr_hs, rot, out, cache, token_seq, positions,             \
+                          page_indptr, page_ids, rows, n_rows, n_heads, page_size, scale, window, num_pages, status,   \
+                          (cudaStream_t)st);                                                                           \
+  }
+
+TKB_LATENT_EXPORTS(f32, float)
+TKB_LATENT_EXPORTS(bf16, __nv_bfloat16)
+TKB_EXPORT int tkb_latent_rank() { return RANK; }

@@ -1,0 +1,286 @@
+// Routed experts (mixture of experts): the router with its choice of the `top` largest logits and the softmax over
+// the chosen ones (float32), the ordering of a step's (token, choice) pairs by expert, the experts' products over
+// that ordering (each block finds its expert from the offsets on the device, so nothing is read back to the host),
+// and the weighted sum of the chosen experts' outputs.  Built for float and bfloat16 activations.
+#include "common.cuh"
+#include <float.h>
+
+using namespace tkb;
+
+namespace {
+
+// ------------------------------------------------------------------------------------------------
+// One warp a token: logits z_e = h . Wr[e] + b[e] in float32 (Wr float32 [E, H]); the `top` largest are taken one
+// after the other (equal logits: the lower expert first); weights = softmax over the chosen logits.
+template <typename T>
+__global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ br,
+                                 const int* __restrict__ token_seq, int* __restrict__ top_idx,
+                                 float* __restrict__ top_w, int n_tokens, int H, int E, int top) {
+  extern __shared__ float z_all[];  // [warps][E]
+  trigger_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= n_tokens) return;
+  if (token_seq != nullptr && token_seq[t] < 0) {
+    for (int k = lane; k < top; k += 32) {
+      top_idx[(size_t)t * top + k] = -1;
+      top_w[(size_t)t * top + k] = 0.f;
+    }
+    return;
+  }
+  float* z = z_all + (size_t)warp * E;
+  const T* hr = h + (size_t)t * H;
+  for (int e = 0; e < E; e++) {
+    const float* w = wr + (size_t)e * H;
+    float acc = 0.f;
+    for (int i = lane; i < H; i += 32) acc = fmaf(to_float(hr[i]), w[i], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) z[e] = acc + (br != nullptr ? br[e] : 0.f);
+  }
+  __syncwarp();
+  float first = 0.f, denom = 0.f;
+  for (int k = 0; k < top; k++) {
+    float best = -FLT_MAX;
+    int arg = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = z[e];
+      if (v > best) { best = v; arg = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+    if (k == 0) first = best;
+    const float p = expf(best - first);
+    denom += p;
+    if (lane == 0) {
+      top_idx[(size_t)t * top + k] = arg;
+      top_w[(size_t)t * top + k] = p;
+      z[arg] = -FLT_MAX;
+    }
+    __syncwarp();
+  }
+  const float inv = 1.f / denom;
+  __syncwarp();
+  for (int k = lane; k < top; k += 32) top_w[(size_t)t * top + k] *= inv;
+}
+
+// One block: offsets[e] .. offsets[e + 1] is expert e's span of the ordering; order[p] is the (token, choice) pair
+// at place p (token * top + choice), place_of[pair] its place (-1 for a padding token's pairs).
+__global__ void moe_order_kernel(const int* __restrict__ top_idx, int n_pairs, int E, int* __restrict__ offsets,
+                                 int* __restrict__ order, int* __restrict__ place_of) {
+  extern __shared__ int cnt[];  // [E] counts, then [E] cursors
+  int* cursor = cnt + E;
+  trigger_dependents();
+  grid_dependency_wait();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int a = threadIdx.x; a < n_pairs; a += blockDim.x) {
+    const int e = top_idx[a];
+    if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < E; e++) {
+      offsets[e] = run;
+      cursor[e] = run;
+      run += cnt[e];
+    }
+    offsets[E] = run;
+  }
+  __syncthreads();
+  for (int a = threadIdx.x; a < n_pairs; a += blockDim.x) {
+    const int e = top_idx[a];
+    if (e >= 0 && e < E) {
+      const int p = atomicAdd(&cursor[e], 1);
+      order[p] = a;
+      place_of[a] = p;
+    } else {
+      place_of[a] = -1;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// The experts' products over the ordering, on the FP32 pipes with float32 sums (each output element is one
+// sequential chain over K, whatever else is in the step):
+//   plain:  C[p, n] = A[src(p), :] . W[e][n, :]                      (C float32 [places, N])
+//   gated:  C[p, n] = silu(A[src(p), :] . W[e][n, :]) * (A[src(p), :] . W[e][N + n, :])      (W[e] is [2N, K])
+// src(p) = order[p] / top if `order` is given (rows of the step's tokens), else p.  Block (x, y): column tile x of the
+// y-th row tile, counted over the experts' spans in turn; blocks beyond the last tile leave at once.
+constexpr int BM = 64, BN = 64, BK = 16;
+
+template <typename TA, typename TC, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ W, TC* __restrict__ C, int ldc,
+                const int* __restrict__ offsets, const int* __restrict__ order, int top, int E, int N, int K) {
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Ws[BK][BN + 4];
+  __shared__ float Us[GATED ? BK : 1][BN + 4];
+  __shared__ int src_row[BM];
+  trigger_dependents();
+  grid_dependency_wait();
+  int tile = blockIdx.y, e = 0, p0 = 0, p1 = 0;
+  for (; e < E; e++) {
+    const int lo = offsets[e], hi = offsets[e + 1];
+    const int tiles = (hi - lo + BM - 1) / BM;
+    if (tile < tiles) {
+      p0 = lo + tile * BM;
+      p1 = hi;
+      break;
+    }
+    tile -= tiles;
+  }
+  if (e >= E) return;
+  const int tid = threadIdx.x;
+  const int n0 = blockIdx.x * BN;
+  if (tid < BM) {
+    const int p = p0 + tid;
+    src_row[tid] = p < p1 ? (order != nullptr ? order[p] / top : p) : -1;
+  }
+  __syncthreads();
+  const TA* We = W + (size_t)e * (GATED ? 2 : 1) * N * K;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int lrow = tid >> 2, lk = (tid & 3) * 4;
+  float acc[4][4], acu[GATED ? 4 : 1][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      acc[i][j] = 0.f;
+      if (GATED) acu[i][j] = 0.f;
+    }
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    const int sr = src_row[lrow];
+    const int n = n0 + lrow;
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      const int k = k0 + lk + u;
+      As[lk + u][lrow] = (sr >= 0 && k < K) ? to_float(A[(size_t)sr * lda + k]) : 0.f;
+      Ws[lk + u][lrow] = (n < N && k < K) ? to_float(We[(size_t)n * K + k]) : 0.f;
+      if (GATED) Us[lk + u][lrow] = (n < N && k < K) ? to_float(We[(size_t)(N + n) * K + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; kk++) {
+      float a[4], b[4], c[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        b[j] = Ws[kk][tx * 4 + j];
+        if (GATED) c[j] = Us[kk][tx * 4 + j];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+          if (GATED) acu[i][j] = fmaf(a[i], c[j], acu[i][j]);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int p = p0 + ty * 4 + i;
+    if (p >= p1) continue;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= N) continue;
+      float v = acc[i][j];
+      if (GATED) v = v / (1.f + expf(-v)) * acu[i][j];
+      C[(size_t)p * ldc + n] = from_float<TC>(v);
+    }
+  }
+}
+
+// out[t] = sum_k top_w[t, k] * y[place_of[t * top + k]]  (+ shared[t]), in choice order, float32 sums, rounded once.
+// shared: [rows, H] in the activation type, or float32 slices [n_slices][rows, H] added in slice order.
+template <typename T>
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place_of,
+                                   const float* __restrict__ top_w, const T* __restrict__ shared_t,
+                                   const float* __restrict__ shared_slices, int n_slices, long long slice_stride,
+                                   T* __restrict__ out, int H, int top) {
+  trigger_dependents();
+  grid_dependency_wait();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; k++) {
+      const int p = place_of[(size_t)t * top + k];
+      if (p >= 0) acc = fmaf(top_w[(size_t)t * top + k], y[(size_t)p * H + i], acc);
+    }
+    if (shared_t != nullptr) acc += to_float(shared_t[(size_t)t * H + i]);
+    for (int s = 0; s < n_slices; s++) acc += shared_slices[(size_t)s * slice_stride + (size_t)t * H + i];
+    out[(size_t)t * H + i] = from_float<T>(acc);
+  }
+}
+
+template <typename T>
+int route_launch(const void* h, const float* wr, const float* br, const int* token_seq, int* top_idx, float* top_w,
+                 int n_tokens, int H, int E, int top, cudaStream_t st) {
+  if (n_tokens <= 0) return 0;
+  if (E <= 0 || top <= 0 || top > E || (size_t)E * 4 * 4 > 48 * 1024) return -2;
+  const int warps = 4;
+  return launch_pdl(moe_route_kernel<T>, dim3((n_tokens + warps - 1) / warps), dim3(warps * 32),
+                    (size_t)warps * E * sizeof(float), st, (const T*)h, wr, br, token_seq, top_idx, top_w, n_tokens, H, E,
+                    top);
+}
+
+template <typename TA, typename TC, bool GATED>
+int gemm_launch(const void* A, int lda, const void* W, void* C, int ldc, const int* offsets, const int* order, int top,
+                int n_places, int E, int N, int K, cudaStream_t st) {
+  if (n_places <= 0 || N <= 0) return 0;
+  if (K <= 0 || E <= 0) return -2;
+  const int row_tiles = n_places / BM + E;  // sum over experts of ceil(count / BM) is at most this
+  if (row_tiles > 65535) return -3;
+  return launch_pdl(moe_gemm_kernel<TA, TC, GATED>, dim3((N + BN - 1) / BN, row_tiles), dim3(256), 0, st, (const TA*)A,
+                    lda, (const TA*)W, (TC*)C, ldc, offsets, order, top, E, N, K);
+}
+
+template <typename T>
+int combine_launch(const float* y, const int* place_of, const float* top_w, const void* shared_t,
+                   const float* shared_slices, int n_slices, long long slice_stride, void* out, int n_tokens, int H,
+                   int top, cudaStream_t st) {
+  if (n_tokens <= 0) return 0;
+  return launch_pdl(moe_combine_kernel<T>, dim3(n_tokens), dim3(H >= 1024 ? 256 : 128), 0, st, y, place_of, top_w,
+                    (const T*)shared_t, shared_slices, n_slices, slice_stride, (T*)out, H, top);
+}
+
+}  // namespace
+
+TKB_EXPORT int tkb_moe_order(const int* top_idx, int n_pairs, int E, int* offsets, int* order, int* place_of, void* st) {
+  if (n_pairs <= 0) return 0;
+  if (E <= 0 || (size_t)E * 8 > 48 * 1024) return -2;
+  return launch_pdl(moe_order_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), (cudaStream_t)st, top_idx, n_pairs,
+                    E, offsets, order, place_of);
+}
+
+#define TKB_MOE_EXPORTS(SUF, T)                                                                                        \
+  TKB_EXPORT int tkb_moe_route_##SUF(const void* h, const float* wr, const float* br, const int* token_seq,            \
+                                     int* top_idx, float* top_w, int n_tokens, int H, int E, int top, void* st) {      \
+    return route_launch<T>(h, wr, br, token_seq, top_idx, top_w, n_tokens, H, E, top, (cudaStream_t)st);               \
+  }                                                                                                                    \
+  TKB_EXPORT int tkb_moe_gemm_gated_##SUF(const void* A, int lda, const void* W, void* C, int ldc, const int* offsets, \
+                                          const int* order, int top, int n_places, int E, int N, int K, void* st) {    \
+    return gemm_launch<T, T, true>(A, lda, W, C, ldc, offsets, order, top, n_places, E, N, K, (cudaStream_t)st);       \
+  }                                                                                                                    \
+  TKB_EXPORT int tkb_moe_gemm_##SUF(const void* A, int lda, const void* W, void* C, int ldc, const int* offsets,       \
+                                    const int* order, int top, int n_places, int E, int N, int K, void* st) {          \
+    return gemm_launch<T, float, false>(A, lda, W, C, ldc, offsets, order, top, n_places, E, N, K, (cudaStream_t)st);  \
+  }                                                                                                                    \
+  TKB_EXPORT int tkb_moe_combine_##SUF(const float* y, const int* place_of, const float* top_w, const void* shared_t,  \
+                                       const float* shared_slices, int n_slices, long long slice_stride, void* out,    \
+                                       int n_tokens, int H, int top, void* st) {                                       \
+    return combine_launch<T>(y, place_of, top_w, shared_t, shared_slices, n_slices, slice_stride, out, n_tokens, H,    \
+                             top, (cudaStream_t)st);                                                                   \
+  }
+
+TKB_MOE_EXPORTS(f32, float)
+TKB_MOE_EXPORTS(bf16, __nv_bfloat16)

@@ -70,6 +70,8 @@ class StepContext:
         self.device = device
         self.n_tokens = int(host.token_ids.shape[0])
         self.n_seqs = int(host.seq_slot.shape[0])
+        # every request brings exactly one token (a decode step): kernels that fuse across a token's row may run
+        self.single_token_step = self.n_tokens == self.n_seqs and bool((host.seq_q_len == 1).all())
         self.all_rows_wanted = (
             host.logit_rows.shape[0] == self.n_tokens
             and bool(np.array_equal(host.logit_rows, np.arange(self.n_tokens, dtype=np.int32)))

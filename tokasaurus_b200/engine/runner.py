@@ -66,8 +66,9 @@ class ModelRunner:
         config.finalize(getattr(self.model_config, "max_position_embeddings", None))
 
         needs = self.model.cache_entries()
-        head_dims = sorted({n.head_dim for n in needs.values() if isinstance(n, PagedCacheNeed)})
+        head_dims = sorted({n.head_dim for n in needs.values() if isinstance(n, PagedCacheNeed) and n.planes == 2})
         ops.prepare(head_dims, self.rt.dtype)
+        ops.prepare_modules(self.model.kernel_modules("float32" if self.rt.dtype == torch.float32 else "bfloat16"))
 
         specs = self.model.weight_specs()
         if config.random_weights is not None:

@@ -122,8 +122,8 @@ def prepare(head_dims=(), dtype: torch.dtype = torch.bfloat16) -> None:
 
 # ---------------------------------------------------------------------------------------------
 def embed_gather(table: torch.Tensor, ids: torch.Tensor, token_seq: torch.Tensor, seq_slot: torch.Tensor,
-                 last_token: torch.Tensor, x_out: torch.Tensor, status: torch.Tensor) -> None:
-    """x_out[t] = table[ids[t]] as float32; ids[t] < 0 takes last_token[seq_slot[token_seq[t]]]."""
+                 last_token: torch.Tensor, x_out: torch.Tensor, status: torch.Tensor, scale: float = 1.0) -> None:
+    """x_out[t] = table[ids[t]] * scale as float32; ids[t] < 0 takes last_token[seq_slot[token_seq[t]]]."""
     _need_cuda(table, ids, token_seq, seq_slot, last_token, x_out, status)
     n, H = x_out.shape
     V = table.shape[0]
@@ -132,7 +132,7 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, token_seq: torch.Tensor
     _need(ids.dtype == torch.int32 and ids.numel() >= n and token_seq.numel() >= n, "embed_gather: ids int32 [T]")
     f = _fn(_libs.get("elementwise.cu"), f"tkb_embed_gather_{_suffix(table.dtype)}")
     _check(f(_ptr(table), _ptr(ids), _ptr(token_seq), _ptr(seq_slot), _ptr(last_token), _ptr(x_out), c_int(n),
-             c_int(H), c_int(V), _ptr(status), _stream()), "embed_gather")
+             c_int(H), c_int(V), c_float(scale), _ptr(status), _stream()), "embed_gather")
 
 
 def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
@@ -696,3 +696,246 @@ def linear(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
 
 def softmax_scale(head_dim: int) -> float:
     return 1.0 / math.sqrt(head_dim)
+
+
+# ---------------------------------------------------------------------------------------------
+# Layer norm, short convolution, PolyNorm (csrc/norm_conv.cu)
+def _split_update(delta: torch.Tensor | None, rows: int, H: int, act_dtype: torch.dtype, what: str):
+    """A residual update as (rows in the activation type | None, float32 slices | None, slices, slice stride)."""
+    if delta is None:
+        return None, None, 0, 0
+    if delta.dim() == 3:
+        _need(delta.dtype == torch.float32 and tuple(delta.shape[1:]) == (rows, H) and delta.is_contiguous(),
+              f"{what}: slices must be contiguous float32 [slices, rows, H]")
+        return None, delta, delta.shape[0], rows * H
+    _need(tuple(delta.shape) == (rows, H) and delta.is_contiguous(), f"{what}: update shape")
+    if delta.dtype == torch.float32 and act_dtype != torch.float32:
+        return None, delta, 1, rows * H
+    _need(delta.dtype == act_dtype, f"{what}: the update is in the activation type or float32")
+    return delta, None, 0, 0
+
+
+def add_layernorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, bias: torch.Tensor, eps: float,
+                  out: torch.Tensor) -> None:
+    """x += delta (float32, in place) if given; out = (x - mean) / sqrt(var + eps) * weight + bias in out's dtype."""
+    _need_cuda(x, delta, weight, bias, out)
+    rows, H = x.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "add_layernorm: x must be contiguous float32")
+    _need(weight.dtype == torch.float32 and weight.numel() == H and bias.dtype == torch.float32 and bias.numel() == H,
+          "add_layernorm: weight and bias must be float32 [H]")
+    _need(out.shape == x.shape and out.is_contiguous(), "add_layernorm: out shape")
+    d, sl, n_sl, stride = _split_update(delta, rows, H, out.dtype, "add_layernorm")
+    f = _fn(_libs.get("norm_conv.cu"), f"tkb_add_layernorm_{_suffix(out.dtype)}")
+    _check(f(_ptr(x), _ptr(d), _ptr(sl), c_int(n_sl), ctypes.c_longlong(stride), _ptr(weight), _ptr(bias), _ptr(out),
+             c_float(eps), c_int(rows), c_int(H), _stream()), "add_layernorm")
+
+
+def add_layernorm_conv1(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, bias: torch.Tensor,
+                        eps: float, conv_w: torch.Tensor, carry: torch.Tensor, token_seq: torch.Tensor,
+                        seq_slot: torch.Tensor, out: torch.Tensor) -> None:
+    """``add_layernorm`` followed by ``short_conv`` for a step in which every request brings one token, in one kernel."""
+    _need_cuda(x, delta, weight, bias, conv_w, carry, token_seq, seq_slot, out)
+    rows, H = x.shape
+    taps = conv_w.shape[1]
+    _need(x.dtype == torch.float32 and x.is_contiguous() and out.shape == x.shape and out.is_contiguous(),
+          "add_layernorm_conv1: x float32, out of the same shape")
+    _need(weight.dtype == torch.float32 and weight.numel() == H and bias.dtype == torch.float32 and bias.numel() == H,
+          "add_layernorm_conv1: weight and bias must be float32 [H]")
+    _need(conv_w.dtype == torch.float32 and conv_w.is_contiguous() and conv_w.shape[0] == H, "add_layernorm_conv1: taps")
+    _need(carry.dtype == torch.float32 and carry.is_contiguous() and tuple(carry.shape[1:]) == (max(taps - 1, 0), H),
+          "add_layernorm_conv1: carried inputs float32 [slots, taps - 1, H]")
+    d, sl, n_sl, stride = _split_update(delta, rows, H, out.dtype, "add_layernorm_conv1")
+    f = _fn(_libs.get("norm_conv.cu"), f"tkb_add_layernorm_conv1_{_suffix(out.dtype)}")
+    _check(f(_ptr(x), _ptr(d), _ptr(sl), c_int(n_sl), ctypes.c_longlong(stride), _ptr(weight), _ptr(bias),
+             _ptr(conv_w), _ptr(carry), _ptr(token_seq), _ptr(seq_slot), _ptr(out), c_float(eps), c_int(rows), c_int(H),
+             c_int(taps), _stream()), "add_layernorm_conv1")
+
+
+def short_conv(h: torch.Tensor, out: torch.Tensor, conv_w: torch.Tensor, carry: torch.Tensor, token_seq: torch.Tensor,
+               seq_slot: torch.Tensor, seq_q_start: torch.Tensor, seq_q_len: torch.Tensor, n_seqs: int) -> None:
+    """out_t = h_t + sum_j conv_w[:, j] * h_(t - taps + 1 + j) over each request's tokens in order; inputs from before
+    the step come from ``carry`` [slots, taps - 1, H] (float32, oldest first), which is then brought forward."""
+    _need_cuda(h, out, conv_w, carry, token_seq, seq_slot, seq_q_start, seq_q_len)
+    n, H = h.shape
+    taps = conv_w.shape[1]
+    _need(h.is_contiguous() and out.is_contiguous() and out.shape == h.shape and out.dtype == h.dtype
+          and out.data_ptr() != h.data_ptr(), "short_conv: out is another tensor of h's shape and type")
+    _need(conv_w.dtype == torch.float32 and conv_w.is_contiguous() and conv_w.shape[0] == H, "short_conv: taps float32 [H, taps]")
+    _need(carry.dtype == torch.float32 and carry.is_contiguous() and tuple(carry.shape[1:]) == (max(taps - 1, 0), H),
+          "short_conv: carried inputs float32 [slots, taps - 1, H]")
+    f = _fn(_libs.get("norm_conv.cu"), f"tkb_short_conv_{_suffix(h.dtype)}")
+    _check(f(_ptr(h), _ptr(out), _ptr(conv_w), _ptr(carry), _ptr(token_seq), _ptr(seq_slot), _ptr(seq_q_start),
+             _ptr(seq_q_len), c_int(n), c_int(n_seqs), c_int(H), c_int(taps), _stream()), "short_conv")
+
+
+def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out = a N(z) + b N(z^2) + c N(z^3) + e per row, N(u) = u / sqrt(mean(u^2) + eps); z float32, coef float32 [4]."""
+    _need_cuda(z, coef, out)
+    rows, F = z.shape
+    _need(z.dtype == torch.float32 and z.is_contiguous() and out.shape == z.shape and out.is_contiguous(),
+          "polynorm: z contiguous float32, out of the same shape")
+    _need(coef.dtype == torch.float32 and coef.numel() == 4, "polynorm: four float32 coefficients")
+    f = _fn(_libs.get("norm_conv.cu"), f"tkb_polynorm_{_suffix(out.dtype)}")
+    _check(f(_ptr(z), _ptr(coef), _ptr(out), c_float(eps), c_int(rows), c_int(F), _stream()), "polynorm")
+
+
+# ---------------------------------------------------------------------------------------------
+# Gated linear recurrence (csrc/recurrence.cu)
+def recurrence_defines(dim: int, vdim: int) -> dict:
+    """The compile-time constants of the recurrence kernel for heads of ``dim`` x ``vdim``."""
+    _need(0 < dim <= 512 and 0 < vdim <= 1024, f"gated recurrence: head sizes up to 512 x 1024, not {dim} x {vdim}")
+    return dict(TKB_REC_DPT=(dim + 7) // 8, TKB_REC_CPT=(vdim + 127) // 128)
+
+
+def gated_recurrence(qfv: torch.Tensor, state: torch.Tensor, f_bias: torch.Tensor, low: torch.Tensor,
+                     norm_w: torch.Tensor, out: torch.Tensor, seq_slot: torch.Tensor, seq_q_start: torch.Tensor,
+                     seq_q_len: torch.Tensor, n_seqs: int, heads: int, dim: int, vdim: int, eps: float,
+                     write_state: bool = True) -> None:
+    """The recurrence S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t over each request's tokens, then an
+    RMS norm of every head's o.  qfv: float32 [T, heads*dim (q) + heads*dim (f) + heads*vdim (v)] raw projections;
+    state: float32 [slots, heads, vdim, dim] (S transposed); out: [T, heads*vdim]."""
+    _need_cuda(qfv, state, f_bias, low, norm_w, out, seq_slot, seq_q_start, seq_q_len)
+    T = qfv.shape[0]
+    _need(qfv.dtype == torch.float32 and qfv.stride(1) == 1 and qfv.shape[1] == heads * (2 * dim + vdim),
+          "gated_recurrence: qfv float32 [T, heads * (2 dim + vdim)]")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, vdim, dim),
+          "gated_recurrence: state float32 [slots, heads, vdim, dim]")
+    for v, n, what in ((f_bias, heads * dim, "gate bias"), (low, heads * dim, "lower bound"), (norm_w, vdim, "norm weight")):
+        _need(v.dtype == torch.float32 and v.is_contiguous() and v.numel() == n, f"gated_recurrence: {what} float32 [{n}]")
+    _need(out.is_contiguous() and tuple(out.shape) == (T, heads * vdim), "gated_recurrence: out [T, heads * vdim]")
+    f = _fn(_libs.get("recurrence.cu", **recurrence_defines(dim, vdim)), f"tkb_gated_recurrence_{_suffix(out.dtype)}")
+    _check(f(_ptr(qfv), c_int(qfv.stride(0)), _ptr(state), _ptr(f_bias), _ptr(low), _ptr(norm_w), _ptr(out),
+             _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), c_int(n_seqs), c_int(heads), c_int(dim), c_int(vdim),
+             c_float(eps), c_int(1 if write_state else 0), _stream()), "gated_recurrence")
+
+
+# ---------------------------------------------------------------------------------------------
+# Attention over cached latents (csrc/latent_attention.cu)
+def latent_prep(proj: torch.Tensor, q_off: int, q_rank: int, q_norm_w: torch.Tensor | None, cq_out: torch.Tensor | None,
+                kv_off: int, rank: int, rot: int, rot_dims: int, kv_norm_w: torch.Tensor | None,
+                inv_freq: torch.Tensor | None, cache: torch.Tensor | None, positions: torch.Tensor,
+                token_seq: torch.Tensor, page_indptr: torch.Tensor, page_ids: torch.Tensor, page_size: int, eps: float,
+                status: torch.Tensor, act_dtype: torch.dtype) -> None:
+    """From float32 projections [T, .]: the RMS-normed query latent (columns q_off..+q_rank) into ``cq_out``; if
+    ``kv_off`` >= 0 the RMS-normed latent (rank columns) and the rotated shared key part (rot columns, the first
+    ``rot_dims`` rotated in interleaved pairs) into the request's cache rows [pages, page_size, rank + rot]."""
+    _need_cuda(proj, q_norm_w, cq_out, kv_norm_w, inv_freq, cache, positions, token_seq, page_indptr, page_ids, status)
+    n = proj.shape[0]
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1, "latent_prep: float32 projections")
+    if q_rank:
+        _need(cq_out is not None and cq_out.is_contiguous() and tuple(cq_out.shape) == (n, q_rank) and cq_out.dtype == act_dtype
+              and q_norm_w is not None and q_norm_w.dtype == torch.float32 and q_norm_w.numel() == q_rank,
+              "latent_prep: query latent output [T, q_rank] and its float32 norm weight")
+    num_pages = 0
+    if kv_off >= 0:
+        _need(cache is not None and cache.is_contiguous() and cache.dtype == act_dtype
+              and tuple(cache.shape[1:]) == (1, page_size, rank + rot), "latent_prep: cache [pages, 1, page_size, rank + rot]")
+        _need(kv_norm_w is not None and kv_norm_w.dtype == torch.float32 and kv_norm_w.numel() == rank, "latent_prep: norm weight")
+        _need(rot_dims == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2),
+              "latent_prep: inv_freq float32 [rot_dims / 2]")
+        num_pages = cache.shape[0]
+    f = _fn(_libs.get("latent_attention.cu", TKB_LAT_RANK=rank), f"tkb_latent_prep_{_suffix(act_dtype)}")
+    _check(f(_ptr(proj), c_int(proj.stride(0)), c_int(q_off), c_int(q_rank), _ptr(q_norm_w), _ptr(cq_out), c_int(kv_off),
+             c_int(rot), c_int(rot_dims), _ptr(kv_norm_w), _ptr(inv_freq), _ptr(cache), _ptr(positions), _ptr(token_seq),
+             _ptr(page_indptr), _ptr(page_ids), c_int(page_size), c_int(num_pages), c_float(eps), c_int(n), _ptr(status),
+             _stream()), "latent_prep")
+
+
+def rotate_pairs(x: torch.Tensor, n_heads: int, head_stride: int, off: int, rot_dims: int, inv_freq: torch.Tensor,
+                 positions: torch.Tensor, token_seq: torch.Tensor, rank: int) -> None:
+    """In place: in every head of every row of x [T, .], the pairs (off + 2i, off + 2i + 1), i < rot_dims / 2, are
+    turned by position * inv_freq[i] (interleaved rotary encoding)."""
+    _need_cuda(x, inv_freq, positions, token_seq)
+    _need(x.stride(1) == 1 and off + rot_dims <= head_stride and n_heads * head_stride <= x.shape[1], "rotate_pairs: layout")
+    _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2, "rotate_pairs: inv_freq float32 [rot_dims / 2]")
+    f = _fn(_libs.get("latent_attention.cu", TKB_LAT_RANK=rank), f"tkb_rotate_pairs_{_suffix(x.dtype)}")
+    _check(f(_ptr(x), c_int(x.stride(0)), c_int(head_stride), c_int(off), c_int(n_heads), c_int(rot_dims), _ptr(inv_freq),
+             _ptr(positions), _ptr(token_seq), c_int(x.shape[0]), _stream()), "rotate_pairs")
+
+
+def latent_attn(q_abs: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, token_seq: torch.Tensor,
+                positions: torch.Tensor, page_indptr: torch.Tensor, page_ids: torch.Tensor, rows: torch.Tensor | None,
+                n_rows: int, page_size: int, scale: float, window: int | None, status: torch.Tensor) -> None:
+    """q_abs [T, heads, rank] and q_rot [T, heads, rot] (any strides with a unit last one); cache
+    [pages, 1, page_size, rank + rot]; out [n_rows, heads, rank]: softmax((q_abs . c + q_rot . k_rot) * scale) over
+    the rows of the last ``window`` positions, times c."""
+    _need_cuda(q_abs, q_rot, out, cache, token_seq, positions, page_indptr, page_ids, rows, status)
+    T, nh, rank = q_abs.shape
+    rot = q_rot.shape[2]
+    _need(q_abs.stride(2) == 1 and q_rot.stride(2) == 1 and q_rot.shape[:2] == q_abs.shape[:2], "latent_attn: q layout")
+    _need(q_abs.dtype == cache.dtype and q_rot.dtype == cache.dtype and out.dtype == cache.dtype, "latent_attn: one type")
+    _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (1, page_size, rank + rot), "latent_attn: cache layout")
+    _need(out.is_contiguous() and tuple(out.shape) == (n_rows, nh, rank), "latent_attn: out [rows, heads, rank]")
+    f = _fn(_libs.get("latent_attention.cu", TKB_LAT_RANK=rank), f"tkb_latent_attn_simt_{_suffix(cache.dtype)}")
+    _check(f(_ptr(q_abs), ctypes.c_longlong(q_abs.stride(0)), ctypes.c_longlong(q_abs.stride(1)), _ptr(q_rot),
+             ctypes.c_longlong(q_rot.stride(0)), ctypes.c_longlong(q_rot.stride(1)), c_int(rot), _ptr(out), _ptr(cache),
+             _ptr(token_seq), _ptr(positions), _ptr(page_indptr), _ptr(page_ids), _ptr(rows), c_int(n_rows), c_int(nh),
+             c_int(page_size), c_float(scale), c_int(window or 0), c_int(cache.shape[0]), _ptr(status), _stream()),
+           "latent_attn")
+
+
+# ---------------------------------------------------------------------------------------------
+# Routed experts (csrc/moe.cu)
+def moe_route(h: torch.Tensor, router_w: torch.Tensor, router_b: torch.Tensor | None, token_seq: torch.Tensor,
+              top: int, top_idx: torch.Tensor, top_w: torch.Tensor) -> None:
+    """Router logits h @ router_w^T + router_b in float32, the ``top`` largest per token (int32 [T, top]) and the
+    softmax over them (float32 [T, top])."""
+    _need_cuda(h, router_w, router_b, token_seq, top_idx, top_w)
+    T, H = h.shape
+    E = router_w.shape[0]
+    _need(h.is_contiguous() and router_w.dtype == torch.float32 and router_w.is_contiguous() and router_w.shape[1] == H,
+          "moe_route: router weight float32 [E, H]")
+    _need(router_b is None or (router_b.dtype == torch.float32 and router_b.numel() == E), "moe_route: bias float32 [E]")
+    _need(top_idx.dtype == torch.int32 and top_w.dtype == torch.float32 and tuple(top_idx.shape) == (T, top)
+          and tuple(top_w.shape) == (T, top) and top_idx.is_contiguous() and top_w.is_contiguous(), "moe_route: outputs [T, top]")
+    f = _fn(_libs.get("moe.cu"), f"tkb_moe_route_{_suffix(h.dtype)}")
+    _check(f(_ptr(h), _ptr(router_w), _ptr(router_b), _ptr(token_seq), _ptr(top_idx), _ptr(top_w), c_int(T), c_int(H),
+             c_int(E), c_int(top), _stream()), "moe_route")
+
+
+def moe_order(top_idx: torch.Tensor, n_experts: int, offsets: torch.Tensor, order: torch.Tensor,
+              place_of: torch.Tensor) -> None:
+    """Order the (token, choice) pairs by expert: offsets int32 [E + 1], order int32 [pairs] (pair at each place),
+    place_of int32 [pairs] (place of each pair, -1 for pairs of padding tokens)."""
+    _need_cuda(top_idx, offsets, order, place_of)
+    n = top_idx.numel()
+    _need(all(t.dtype == torch.int32 and t.is_contiguous() for t in (top_idx, offsets, order, place_of)), "moe_order: int32")
+    _need(offsets.numel() == n_experts + 1 and order.numel() == n and place_of.numel() == n, "moe_order: sizes")
+    _check(_fn(_libs.get("moe.cu"), "tkb_moe_order")(_ptr(top_idx), c_int(n), c_int(n_experts), _ptr(offsets), _ptr(order),
+                                                     _ptr(place_of), _stream()), "moe_order")
+
+
+def moe_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor | None,
+             top: int, gated: bool) -> None:
+    """The experts' products over the ordering.  w [E, N (2N if gated), K]; a [., K]; row p of ``out`` is made from
+    row order[p] // top of ``a`` (row p if ``order`` is None) with the weights of the expert whose span holds p.
+    gated: out = silu(a w_gate^T) * (a w_up^T) in a's type [places, N]; else float32 [places, N]."""
+    _need_cuda(a, w, out, offsets, order)
+    E, NN, K = w.shape
+    N = NN // 2 if gated else NN
+    _need(a.dtype == w.dtype and a.stride(1) == 1 and a.shape[1] == K and w.is_contiguous(), "moe_gemm: operands")
+    _need(out.shape[1] == N and out.stride(1) == 1 and out.dtype == (a.dtype if gated else torch.float32), "moe_gemm: out")
+    name = f"tkb_moe_gemm_{'gated_' if gated else ''}{_suffix(a.dtype)}"
+    _check(_fn(_libs.get("moe.cu"), name)(_ptr(a), c_int(a.stride(0)), _ptr(w), _ptr(out), c_int(out.stride(0)),
+                                          _ptr(offsets), _ptr(order), c_int(top), c_int(out.shape[0]), c_int(E), c_int(N),
+                                          c_int(K), _stream()), "moe_gemm")
+
+
+def moe_combine(y: torch.Tensor, place_of: torch.Tensor, top_w: torch.Tensor, shared: torch.Tensor | None,
+                out: torch.Tensor) -> None:
+    """out[t] = sum_k top_w[t, k] * y[place_of[t, k]] (+ shared[t]); y float32 [places, H]; shared [T, H] in out's type
+    or float32 slices [slices, T, H]."""
+    _need_cuda(y, place_of, top_w, shared, out)
+    T, H = out.shape
+    top = top_w.shape[1]
+    _need(y.dtype == torch.float32 and y.is_contiguous() and y.shape[1] == H and out.is_contiguous(), "moe_combine: y, out")
+    d, sl, n_sl, stride = _split_update(shared, T, H, out.dtype, "moe_combine")
+    f = _fn(_libs.get("moe.cu"), f"tkb_moe_combine_{_suffix(out.dtype)}")
+    _check(f(_ptr(y), _ptr(place_of), _ptr(top_w), _ptr(d), _ptr(sl), c_int(n_sl), ctypes.c_longlong(stride), _ptr(out),
+             c_int(T), c_int(H), c_int(top), _stream()), "moe_combine")
+
+
+def prepare_modules(modules) -> None:
+    """Build and load the listed (source file, constants) modules."""
+    for source, defines in modules:
+        _libs.get(source, **(defines or {}))

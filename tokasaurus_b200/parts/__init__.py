@@ -1,5 +1,6 @@
 from tokasaurus_b200.parts.base import (  # noqa: F401
     FeedForward,
+    InputStage,
     Mixer,
     Norm,
     PagedCacheNeed,
@@ -10,10 +11,13 @@ from tokasaurus_b200.parts.base import (  # noqa: F401
     StateNeed,
     WeightSpec,
 )
-from tokasaurus_b200.parts.norm import RMSNorm  # noqa: F401
+from tokasaurus_b200.parts.norm import LayerNorm, RMSNorm  # noqa: F401
+from tokasaurus_b200.parts.conv import ShortConv  # noqa: F401
 from tokasaurus_b200.parts.rope import NoPositionEncoding, RotaryEncoding  # noqa: F401
 from tokasaurus_b200.parts.attention import PagedAttention  # noqa: F401
-from tokasaurus_b200.parts.mlp import GatedMLP  # noqa: F401
+from tokasaurus_b200.parts.mlp import GatedMLP, PolyNormMLP, RoutedExperts  # noqa: F401
+from tokasaurus_b200.parts.recurrent import GatedLinearRecurrence  # noqa: F401
+from tokasaurus_b200.parts.latent_attention import LatentAttention  # noqa: F401
 from tokasaurus_b200.parts.block import PreNormBlock  # noqa: F401
 from tokasaurus_b200.parts.embedding import OutputHead, TokenEmbedding  # noqa: F401
 from tokasaurus_b200.parts.model import DecoderModel, LayerCall  # noqa: F401

@@ -43,11 +43,13 @@ class WeightSpec:
 @dataclass(frozen=True)
 class PagedCacheNeed:
     """Per-token keys and values kept in pages.  ``window``: only the last ``window`` keys
-    (the query's own included) are ever read, so pages behind it can be given back."""
+    (the query's own included) are ever read, so pages behind it can be given back.  ``planes``: 2 for keys and
+    values, 1 for a mixer that keeps one row a token (a latent from which it makes both)."""
 
     n_kv_heads: int
     head_dim: int
     window: int | None = None
+    planes: int = 2
 
 
 @dataclass(frozen=True)
@@ -76,6 +78,11 @@ class QkvStage:
 
 class Part:
     def weight_specs(self) -> Sequence[WeightSpec]:
+        return ()
+
+    def kernel_modules(self, dtype: str) -> Sequence[tuple[str, dict | None]]:
+        """The (source file, compile-time constants) kernel modules this part launches in an engine of precision
+        ``dtype`` ("bfloat16" or "float32"), beyond those every model needs: a first call builds these and no more."""
         return ()
 
     def bind(self, weights: Mapping[str, "torch.Tensor"], rt: "Runtime") -> None:
@@ -132,6 +139,18 @@ class Mixer(Part):
 
 class FeedForward(Part):
     def forward(self, ctx: "StepContext", h: "torch.Tensor") -> "torch.Tensor":
+        raise NotImplementedError
+
+
+class InputStage(Part):
+    """What stands between a norm and the sublayer that reads it (a short convolution over time, for instance).
+    It may keep a state per request (``state_need``), which the cache manager holds in the request's slot."""
+
+    def state_need(self) -> StateNeed | None:
+        return None
+
+    def forward(self, ctx: "StepContext", h: "torch.Tensor", state) -> "torch.Tensor":
+        """``h`` [T, width] -> [T, width]; ``state``: the ``StateLayerCache`` of this stage in this layer call."""
         raise NotImplementedError
 
 

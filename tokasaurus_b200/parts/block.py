@@ -1,43 +1,90 @@
 """Arrangement of a mixer and a feed-forward in one block: pre-norm with residual sums,
 ``x = x + mixer(norm1(x)); x = x + ffn(norm2(x))`` (tokasaurus/model/llama.py:342-359 with the
 norms at :230 and :325 and the sums at :284 and :336).  The sums are carried in the float32
-residual stream and are folded into the norm kernel that follows them."""
+residual stream and are folded into the norm kernel that follows them.
+
+Optionally an input stage (``parts.base.InputStage``, a short convolution for instance) stands between each norm
+and the sublayer that reads it, and the feed-forward may be left out (``ffn=None``: the block is its mixer alone).
+A stage's per-request state is a cache entry of the layer call, beside the mixer's."""
 
 from __future__ import annotations
 
 import torch
 
 from tokasaurus_b200.kernels import ops
-from tokasaurus_b200.parts.base import FeedForward, Mixer, Norm, Part, ResidualStream
+from tokasaurus_b200.parts.base import FeedForward, InputStage, Mixer, Norm, Part, ResidualStream
 
 
 class PreNormBlock(Part):
-    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, ffn: FeedForward):
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm | None, ffn: FeedForward | None,
+                 mixer_stage: InputStage | None = None, ffn_stage: InputStage | None = None):
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a block has a feed-forward and its norm, or neither")
+        if ffn is None and ffn_stage is not None:
+            raise ValueError("an input stage of the feed-forward needs a feed-forward")
         self.mixer_norm = mixer_norm
         self.mixer = mixer
         self.ffn_norm = ffn_norm
         self.ffn = ffn
+        self.mixer_stage = mixer_stage
+        self.ffn_stage = ffn_stage
 
     def parts(self):
-        return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+        return tuple(p for p in (self.mixer_norm, self.mixer_stage, self.mixer, self.ffn_norm, self.ffn_stage, self.ffn)
+                     if p is not None)
 
     def weight_specs(self):
         return tuple(s for p in self.parts() for s in p.weight_specs())
+
+    def kernel_modules(self, dtype):
+        return tuple(m for p in self.parts() for m in p.kernel_modules(dtype))
 
     def bind(self, weights, rt) -> None:
         for p in self.parts():
             p.bind(weights, rt)
 
-    def forward(self, ctx, stream: ResidualStream, cache, out_rows=None) -> ResidualStream:
-        """``out_rows`` (int32 device tensor or None): only these rows are needed after the mixer
+    def state_needs(self) -> dict:
+        """{name: StateNeed} of the input stages: state a layer call holds beside its mixer's cache entry."""
+        out = {}
+        for name, stage in (("mixer_stage", self.mixer_stage), ("ffn_stage", self.ffn_stage)):
+            need = stage.state_need() if stage is not None else None
+            if need is not None:
+                out[name] = need
+        return out
+
+    @staticmethod
+    def _staged(ctx, norm, stage, stream, state):
+        if stage is None:
+            return norm.forward(ctx, stream)
+        if hasattr(stage, "forward_with_norm"):
+            return stage.forward_with_norm(ctx, norm, stream, state)
+        return stage.forward(ctx, norm.forward(ctx, stream), state)
+
+    def forward(self, ctx, stream: ResidualStream, cache, out_rows=None, stage_state=None) -> ResidualStream:
+        """``out_rows`` (int32 device tensor or None): only these rows are needed after the block
         (the last block of a step: tokasaurus/model/llama.py:273-278); the stream that comes back
-        then has len(out_rows) rows."""
-        h = self.mixer_norm.forward(ctx, stream)
-        if out_rows is not None:
-            x = torch.empty((out_rows.numel(), stream.x.shape[1]), dtype=stream.x.dtype, device=stream.x.device)
-            ops.gather_rows(stream.x, out_rows, x)
-            stream = ResidualStream(x)
-        stream.delta = self.mixer.forward(ctx, h, cache, out_rows)
-        h = self.ffn_norm.forward(ctx, stream)
+        then has len(out_rows) rows.  ``stage_state``: {name: StateLayerCache} for ``state_needs``."""
+        stage_state = stage_state or {}
+        h = self._staged(ctx, self.mixer_norm, self.mixer_stage, stream, stage_state.get("mixer_stage"))
+        # an input stage of the feed-forward sees every token (its state moves with each), so the rows are cut
+        # only after it
+        cut_late = self.ffn_stage is not None and out_rows is not None
+        if out_rows is not None and not cut_late:
+            stream = self._cut(stream, out_rows)
+        stream.delta = self.mixer.forward(ctx, h, cache, None if cut_late else out_rows)
+        if self.ffn is None:
+            return stream
+        h = self._staged(ctx, self.ffn_norm, self.ffn_stage, stream, stage_state.get("ffn_stage"))
+        if cut_late:
+            stream = self._cut(stream, out_rows)
+            hc = torch.empty((out_rows.numel(), h.shape[1]), dtype=h.dtype, device=h.device)
+            ops.gather_rows(h, out_rows, hc)
+            h = hc
         stream.delta = self.ffn.forward(ctx, h)
         return stream
+
+    @staticmethod
+    def _cut(stream: ResidualStream, rows) -> ResidualStream:
+        x = torch.empty((rows.numel(), stream.x.shape[1]), dtype=stream.x.dtype, device=stream.x.device)
+        ops.gather_rows(stream.x, rows, x)
+        return ResidualStream(x)

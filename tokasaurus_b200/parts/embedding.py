@@ -10,10 +10,12 @@ from tokasaurus_b200.parts.base import Norm, Part, ResidualStream, WeightSpec
 
 
 class TokenEmbedding(Part):
-    def __init__(self, vocab: int, width: int, weight_name: str):
+    def __init__(self, vocab: int, width: int, weight_name: str, scale: float = 1.0):
+        """``scale`` multiplies the gathered rows (in float32, on their way into the residual stream)."""
         self.vocab = vocab
         self.width = width
         self.weight_name = weight_name
+        self.scale = float(scale)
         self.table: torch.Tensor | None = None
 
     def weight_specs(self):
@@ -24,7 +26,8 @@ class TokenEmbedding(Part):
 
     def forward(self, ctx) -> ResidualStream:
         x = torch.empty((ctx.n_tokens, self.width), dtype=torch.float32, device=self.table.device)
-        ops.embed_gather(self.table, ctx.token_ids, ctx.token_seq, ctx.seq_slot, ctx.last_token, x, ctx.status)
+        ops.embed_gather(self.table, ctx.token_ids, ctx.token_seq, ctx.seq_slot, ctx.last_token, x, ctx.status,
+                         self.scale)
         return ResidualStream(x)
 
 
@@ -41,6 +44,9 @@ class OutputHead(Part):
 
     def weight_specs(self):
         return tuple(self.norm.weight_specs()) + (WeightSpec(self.weight_name, (self.vocab, self.width)),)
+
+    def kernel_modules(self, dtype):
+        return tuple(self.norm.kernel_modules(dtype))
 
     def bind(self, weights, rt) -> None:
         self.norm.bind(weights, rt)

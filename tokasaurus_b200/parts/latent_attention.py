@@ -1,0 +1,107 @@
+"""Attention whose keys and values are made from a small per-token latent ("latent attention").
+
+Per token the mixer makes  c = rmsnorm(W_dkv h)[:rank] * w  and one rotated key part  k_rot = rotate(W_dkv h)[rank:]
+shared by all heads; only this row [c | k_rot] is cached (one plane, one "head" of rank + rot values a token).
+A head's key is [W_uk c | k_rot], its value W_uv c; queries come through a latent of their own,
+q = W_uq rmsnorm(W_dq h), laid out head by head as [dim plain | rot rotated].  The score is
+(q_plain . k_plain + q_rot . k_rot) * scale over the last ``window`` positions (all if None), softmax, W_o.
+
+The engine never expands keys or values: with  q_abs = W_uk^T q_plain  the score is  q_abs . c + q_rot . k_rot  and
+the weighted sum of values is  W_uv (sum_j p_j c_j), so the attention kernel reads the cached rows as they are, the
+same rows for every head.  The rotation pairs dimension 2i with 2i + 1 (interleaved) on the first ``rot_dims``
+values of the rotated part.  A mixer with ``own_kv=False`` has no W_dkv and reads the rows another layer call wrote
+(the model's run order gives it that call's cache entry).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from tokasaurus_b200.kernels import ops
+from tokasaurus_b200.parts.base import Mixer, PagedCacheNeed, WeightSpec
+
+
+class LatentAttention(Mixer):
+    graph_safe = True
+
+    def __init__(self, width: int, n_heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, q_rank: int,
+                 scale: float, rot_base: float, rot_dims: int, norm_eps: float, window: int | None, names: dict,
+                 own_kv: bool = True):
+        """``names``: tensors dq, dq_norm, uq, dkv, dkv_norm (both unused without ``own_kv``), uk, uv, o."""
+        if rot_dims > rot_dim or rot_dims % 2:
+            raise ValueError(f"rot_dims={rot_dims} must be even and at most rot_dim={rot_dim}")
+        self.width, self.n_heads, self.dim, self.rot_dim, self.vdim = width, n_heads, dim, rot_dim, vdim
+        self.kv_rank, self.q_rank = kv_rank, q_rank
+        self.scale, self.rot_base, self.rot_dims = float(scale), float(rot_base), int(rot_dims)
+        self.norm_eps = float(norm_eps)
+        self.window = window
+        self.names = dict(names)
+        self.own_kv = own_kv
+
+    def weight_specs(self):
+        n, H = self.names, self.n_heads
+        specs = [
+            WeightSpec(n["dq"], (self.q_rank, self.width)), WeightSpec(n["dq_norm"], (self.q_rank,), role="vector"),
+            WeightSpec(n["uq"], (H * (self.dim + self.rot_dim), self.q_rank)),
+            WeightSpec(n["uk"], (H * self.dim, self.kv_rank)), WeightSpec(n["uv"], (H * self.vdim, self.kv_rank)),
+            WeightSpec(n["o"], (self.width, H * self.vdim)),
+        ]
+        if self.own_kv:
+            specs += [WeightSpec(n["dkv"], (self.kv_rank + self.rot_dim, self.width)),
+                      WeightSpec(n["dkv_norm"], (self.kv_rank,), role="vector")]
+        return tuple(specs)
+
+    def kernel_modules(self, dtype):
+        mods = [("latent_attention.cu", {"TKB_LAT_RANK": self.kv_rank})]
+        return tuple(mods)
+
+    def cache_need(self):
+        return PagedCacheNeed(1, self.kv_rank + self.rot_dim, self.window, planes=1)
+
+    def bind(self, weights, rt) -> None:
+        n, H = self.names, self.n_heads
+        down = [weights[n["dq"]]] + ([weights[n["dkv"]]] if self.own_kv else [])
+        self.w_down = torch.cat(down, dim=0).contiguous()
+        self.dq_norm = weights[n["dq_norm"]].contiguous()
+        self.dkv_norm = weights[n["dkv_norm"]].contiguous() if self.own_kv else None
+        self.w_uq = weights[n["uq"]].contiguous()
+        # per head: W_uk[h] is [dim, rank], so q_plain[h] @ W_uk[h] folds the key up-projection into the query;
+        # the FP32 product wants its second operand as [N, K] = [rank, dim]
+        self.w_uk = weights[n["uk"]].view(H, self.dim, self.kv_rank).contiguous()
+        self.w_uk_t = self.w_uk.transpose(1, 2).contiguous() if rt.dtype == torch.float32 else None
+        self.w_uv = weights[n["uv"]].view(H, self.vdim, self.kv_rank).contiguous()
+        self.w_o = weights[n["o"]].contiguous()
+        i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
+        self.inv_freq = (self.rot_base ** (-2.0 * i / max(self.rot_dims, 1))).to(torch.float32).to(rt.device)
+        self.dtype = rt.dtype
+
+    def forward(self, ctx, h, cache, out_rows=None):
+        T, H, R, rd, dim = h.shape[0], self.n_heads, self.kv_rank, self.rot_dim, self.dim
+        tables = ctx.tables[cache.group]
+        proj = ops.linear(h, self.w_down, out_dtype=torch.float32)  # [T, q_rank (+ rank + rot)]
+        cq = torch.empty((T, self.q_rank), dtype=h.dtype, device=h.device)
+        write = self.own_kv and cache.writable
+        ops.latent_prep(proj, 0, self.q_rank, self.dq_norm, cq, self.q_rank if write else -1, R, rd, self.rot_dims,
+                        self.dkv_norm, self.inv_freq, cache.k if write else None, ctx.positions, ctx.token_seq,
+                        tables.indptr, tables.page_ids, cache.page_size, self.norm_eps, ctx.status, h.dtype)
+        q = ops.linear(cq, self.w_uq)  # [T, H * (dim + rot)]
+        if self.rot_dims:
+            ops.rotate_pairs(q, H, dim + rd, dim, self.rot_dims, self.inv_freq, ctx.positions, ctx.token_seq, R)
+        q3 = q.view(T, H, dim + rd)
+        q_abs = torch.empty((T, H, R), dtype=h.dtype, device=h.device)
+        if h.dtype == torch.float32:
+            for hh in range(H):
+                ops.sgemm_tn(q3[:, hh, :dim], self.w_uk_t[hh], q_abs[:, hh, :])
+        else:
+            torch.bmm(q3[:, :, :dim].transpose(0, 1), self.w_uk, out=q_abs.transpose(0, 1))
+        n_rows = T if out_rows is None else out_rows.numel()
+        o_lat = torch.empty((n_rows, H, R), dtype=h.dtype, device=h.device)
+        ops.latent_attn(q_abs, q3[:, :, dim:], o_lat, cache.k, ctx.token_seq, ctx.positions, tables.indptr,
+                        tables.page_ids, out_rows, n_rows, cache.page_size, self.scale, self.window, ctx.status)
+        val = torch.empty((n_rows, H, self.vdim), dtype=h.dtype, device=h.device)
+        if h.dtype == torch.float32:
+            for hh in range(H):
+                ops.sgemm_tn(o_lat[:, hh, :], self.w_uv[hh], val[:, hh, :])
+        else:
+            torch.bmm(o_lat.transpose(0, 1), self.w_uv.transpose(1, 2), out=val.transpose(0, 1))
+        return ops.linear(val.view(n_rows, H * self.vdim), self.w_o)

@@ -57,3 +57,97 @@ class GatedMLP(FeedForward):
         if ops.can_use_few_rows(act, self.w_down):
             return ops.linear_few_rows(act, self.w_down, status)
         return ops.linear(act, self.w_down)
+
+
+class PolyNormMLP(FeedForward):
+    """``down(act(up(h)))`` with the PolyNorm activation ``act(z) = a N(z) + b N(z^2) + c N(z^3) + e``, where powers
+    are taken element by element and N divides a token's vector of inner values by its root mean square
+    (``x / sqrt(mean(x^2) + eps)``).  The four numbers are a tensor of the model.  The norms are float32: the up
+    product's float32 result goes straight into the activation kernel."""
+
+    def __init__(self, width: int, inner: int, eps: float, up_name: str, down_name: str, coef_name: str):
+        self.width, self.inner, self.eps = width, inner, float(eps)
+        self.names = (up_name, down_name, coef_name)
+
+    def weight_specs(self):
+        u, d, c = self.names
+        return (WeightSpec(u, (self.inner, self.width)), WeightSpec(d, (self.width, self.inner)),
+                WeightSpec(c, (4,), role="vector"))
+
+    def kernel_modules(self, dtype):
+        return (("norm_conv.cu", None),)
+
+    def bind(self, weights, rt) -> None:
+        u, d, c = self.names
+        self.w_up = weights[u].contiguous()
+        self.w_down = weights[d].contiguous()
+        self.coef = weights[c].contiguous()
+
+    def forward(self, ctx, h):
+        z = ops.linear(h, self.w_up, out_dtype=torch.float32)
+        act = torch.empty(z.shape, dtype=h.dtype, device=h.device)
+        ops.polynorm(z, self.coef, self.eps, act)
+        return ops.linear(act, self.w_down)
+
+
+class RoutedExperts(FeedForward):
+    """A mixture of small SiLU-gated feed-forwards: a router (logits in float32, with a bias) picks each token's
+    ``top`` experts by the largest logits and weighs them by the softmax over the chosen logits; the output is the
+    weighted sum of their outputs, plus a shared expert (any ``FeedForward``) that every token runs through.
+
+    A step's (token, choice) pairs are ordered by expert on the device, and the experts' products run over that
+    ordering with each block looking its expert up; nothing about the routing is read back to the host."""
+
+    def __init__(self, width: int, inner: int, n_experts: int, top: int, router_name: str, router_bias_name: str | None,
+                 expert_names, shared: FeedForward | None = None):
+        """``expert_names(e)`` -> (gate, up, down) tensor names of expert e."""
+        if not 0 < top <= n_experts:
+            raise ValueError(f"top={top} of {n_experts} experts")
+        self.width, self.inner, self.n_experts, self.top = width, inner, n_experts, top
+        self.router_name, self.router_bias_name = router_name, router_bias_name
+        self.expert_names = [tuple(expert_names(e)) for e in range(n_experts)]
+        self.shared = shared
+
+    def weight_specs(self):
+        specs = [WeightSpec(self.router_name, (self.n_experts, self.width), role="vector")]
+        if self.router_bias_name is not None:
+            specs.append(WeightSpec(self.router_bias_name, (self.n_experts,), role="vector"))
+        for g, u, d in self.expert_names:
+            specs += [WeightSpec(g, (self.inner, self.width)), WeightSpec(u, (self.inner, self.width)),
+                      WeightSpec(d, (self.width, self.inner))]
+        if self.shared is not None:
+            specs += list(self.shared.weight_specs())
+        return tuple(specs)
+
+    def kernel_modules(self, dtype):
+        return (("moe.cu", None),) + (tuple(self.shared.kernel_modules(dtype)) if self.shared is not None else ())
+
+    def bind(self, weights, rt) -> None:
+        self.router_w = weights[self.router_name].contiguous()
+        self.router_b = weights[self.router_bias_name].contiguous() if self.router_bias_name is not None else None
+        # [E, 2 * inner, width]: each expert's gate rows, then its up rows;  [E, width, inner]
+        self.w_gate_up = torch.stack([torch.cat([weights[g], weights[u]], dim=0) for g, u, _ in self.expert_names]).contiguous()
+        self.w_down = torch.stack([weights[d] for _, _, d in self.expert_names]).contiguous()
+        if self.shared is not None:
+            self.shared.bind(weights, rt)
+
+    def forward(self, ctx, h):
+        T, dev = h.shape[0], h.device
+        top, E = self.top, self.n_experts
+        top_idx = torch.empty((T, top), dtype=torch.int32, device=dev)
+        top_w = torch.empty((T, top), dtype=torch.float32, device=dev)
+        # rows of padding tokens (a step graph's) choose nothing; a cut-down set of rows has none
+        token_seq = ctx.token_seq if (ctx is not None and T == ctx.n_tokens) else None
+        ops.moe_route(h, self.router_w, self.router_b, token_seq, top, top_idx, top_w)
+        offsets = torch.empty((E + 1,), dtype=torch.int32, device=dev)
+        order = torch.empty((T * top,), dtype=torch.int32, device=dev)
+        place_of = torch.empty((T * top,), dtype=torch.int32, device=dev)
+        ops.moe_order(top_idx, E, offsets, order, place_of)
+        act = torch.empty((T * top, self.inner), dtype=h.dtype, device=dev)
+        ops.moe_gemm(h, self.w_gate_up, act, offsets, order, top, gated=True)
+        y = torch.empty((T * top, self.width), dtype=torch.float32, device=dev)
+        ops.moe_gemm(act, self.w_down, y, offsets, None, top, gated=False)
+        shared = self.shared.forward(ctx, h) if self.shared is not None else None
+        out = torch.empty((T, self.width), dtype=h.dtype, device=dev)
+        ops.moe_combine(y, place_of, top_w, shared, out)
+        return out

@@ -45,6 +45,19 @@ class DecoderModel(Part):
         for c in self.run_order:
             if not c.write_cache and c.cache not in writers:
                 raise ValueError(f"a layer call reads cache entry {c.cache} that no call writes")
+        # state that a block's input stages keep per request: an entry of its own for every layer call and stage
+        # (a block named in two calls runs over two different streams), numbered behind the mixers' entries
+        nxt = max([c.cache for c in self.run_order], default=-1) + 1
+        self.stage_entries: list[dict[str, int]] = []
+        self._stage_needs: dict[int, object] = {}
+        for c in self.run_order:
+            names = {}
+            needs = self.blocks[c.block].state_needs() if hasattr(self.blocks[c.block], "state_needs") else {}
+            for name, need in needs.items():
+                names[name] = nxt
+                self._stage_needs[nxt] = need
+                nxt += 1
+            self.stage_entries.append(names)
 
     @property
     def vocab(self) -> int:
@@ -62,6 +75,13 @@ class DecoderModel(Part):
     def bind(self, weights, rt) -> None:
         for part in [self.embedding, *self.blocks, self.head]:
             part.bind(weights, rt)
+
+    def kernel_modules(self, dtype):
+        seen: dict = {}
+        for part in [self.embedding, *self.blocks, self.head]:
+            for source, defines in part.kernel_modules(dtype):
+                seen.setdefault((source, tuple(sorted((defines or {}).items()))), (source, defines))
+        return tuple(seen.values())
 
     @property
     def graph_safe(self) -> bool:
@@ -87,6 +107,7 @@ class DecoderModel(Part):
             if c.cache in needs and needs[c.cache] != need:
                 raise ValueError(f"cache entry {c.cache} is shared by mixers with different needs")
             needs[c.cache] = need
+        needs.update(self._stage_needs)
         return needs
 
     def forward(self, ctx) -> torch.Tensor:
@@ -96,5 +117,9 @@ class DecoderModel(Part):
         rows = None if ctx.all_rows_wanted else ctx.logit_rows
         for i, call in enumerate(self.run_order):
             cache = ctx.layer_cache(call.cache, call.write_cache)
-            stream = self.blocks[call.block].forward(ctx, stream, cache, rows if i == last else None)
+            if self.stage_entries[i]:
+                states = {name: ctx.layer_cache(entry) for name, entry in self.stage_entries[i].items()}
+                stream = self.blocks[call.block].forward(ctx, stream, cache, rows if i == last else None, states)
+            else:
+                stream = self.blocks[call.block].forward(ctx, stream, cache, rows if i == last else None)
         return self.head.forward(ctx, stream)

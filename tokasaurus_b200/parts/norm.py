@@ -34,3 +34,35 @@ class RMSNorm(Norm):
         out = self._run(stream.x, stream.delta)
         stream.delta = None
         return out
+
+
+class LayerNorm(Norm):
+    """``y = (x - mean) / sqrt(var + eps) * weight + bias`` with ``var = mean((x - mean)^2)``, statistics in float32;
+    the kernel folds the residual add in like ``RMSNorm``'s."""
+
+    def __init__(self, width: int, eps: float, weight_name: str, bias_name: str):
+        self.width = width
+        self.eps = float(eps)
+        self.weight_name = weight_name
+        self.bias_name = bias_name
+        self.weight: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
+        self.out_dtype: torch.dtype | None = None
+
+    def weight_specs(self):
+        return (WeightSpec(self.weight_name, (self.width,), role="vector"),
+                WeightSpec(self.bias_name, (self.width,), role="vector"))
+
+    def kernel_modules(self, dtype):
+        return (("norm_conv.cu", None),)
+
+    def bind(self, weights, rt) -> None:
+        self.weight = weights[self.weight_name]
+        self.bias = weights[self.bias_name]
+        self.out_dtype = rt.dtype
+
+    def forward(self, ctx, stream: ResidualStream):
+        out = torch.empty(stream.x.shape, dtype=self.out_dtype, device=stream.x.device)
+        ops.add_layernorm(stream.x, stream.delta, self.weight, self.bias, self.eps, out)
+        stream.delta = None
+        return out

@@ -1,0 +1,64 @@
+"""A mixer that carries a matrix state per head instead of keys and values: a gated linear recurrence in the HGRN2
+form, where the forget gate also decides what is written,
+
+    S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T,        o_t = S_t^T q_t,
+    q = silu(W_q h),   v = W_v h,   f = low + (1 - low) * sigmoid(W_f h + b_f),
+
+followed by an RMS norm of every head's o_t over its ``vdim`` values (one weight vector shared by the heads) and
+the output projection.  The state is float32, starts at zero and lives in the request's slot; gates, sums and the
+norm are float32 whatever the engine's precision.  The three projections are one matrix product with a float32 result.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from tokasaurus_b200.kernels import ops
+from tokasaurus_b200.parts.base import Mixer, StateNeed, WeightSpec
+
+
+class GatedLinearRecurrence(Mixer):
+    graph_safe = True
+
+    def __init__(self, width: int, n_heads: int, dim: int, vdim: int, norm_eps: float, q_name: str, f_name: str,
+                 f_bias_name: str, lower_name: str, v_name: str, norm_name: str, o_name: str):
+        self.width, self.n_heads, self.dim, self.vdim = width, n_heads, dim, vdim
+        self.norm_eps = float(norm_eps)
+        self.names = dict(q=q_name, f=f_name, f_bias=f_bias_name, lower=lower_name, v=v_name, norm=norm_name, o=o_name)
+        ops.recurrence_defines(dim, vdim)  # refuses sizes the kernel does not take
+        self.w_qfv: torch.Tensor | None = None
+        self.w_o: torch.Tensor | None = None
+
+    def weight_specs(self):
+        n, H, d, v = self.names, self.n_heads, self.dim, self.vdim
+        return (
+            WeightSpec(n["q"], (H * d, self.width)), WeightSpec(n["f"], (H * d, self.width)),
+            WeightSpec(n["v"], (H * v, self.width)), WeightSpec(n["o"], (self.width, H * v)),
+            WeightSpec(n["f_bias"], (H * d,), role="vector"), WeightSpec(n["lower"], (H * d,), role="vector"),
+            WeightSpec(n["norm"], (v,), role="vector"),
+        )
+
+    def kernel_modules(self, dtype):
+        return (("recurrence.cu", ops.recurrence_defines(self.dim, self.vdim)),)
+
+    def cache_need(self):
+        return StateNeed((self.n_heads, self.vdim, self.dim), "float32")  # S transposed: [head][value][key channel]
+
+    def bind(self, weights, rt) -> None:
+        n = self.names
+        self.w_qfv = torch.cat([weights[n["q"]], weights[n["f"]], weights[n["v"]]], dim=0).contiguous()
+        self.w_o = weights[n["o"]].contiguous()
+        self.f_bias = weights[n["f_bias"]].contiguous()
+        self.lower = weights[n["lower"]].contiguous()
+        self.norm_w = weights[n["norm"]].contiguous()
+
+    def forward(self, ctx, h, cache, out_rows=None):
+        qfv = ops.linear(h, self.w_qfv, out_dtype=torch.float32)
+        o = torch.empty((h.shape[0], self.n_heads * self.vdim), dtype=h.dtype, device=h.device)
+        ops.gated_recurrence(qfv, cache.state, self.f_bias, self.lower, self.norm_w, o, ctx.seq_slot, ctx.seq_q_start,
+                             ctx.seq_q_len, ctx.n_seqs, self.n_heads, self.dim, self.vdim, self.norm_eps, cache.writable)
+        if out_rows is not None:
+            cut = torch.empty((out_rows.numel(), o.shape[1]), dtype=o.dtype, device=o.device)
+            ops.gather_rows(o, out_rows, cut)
+            o = cut
+        return ops.linear(o, self.w_o)
