@@ -238,6 +238,14 @@ class CacheManager:
             return StateLayerCache(self._state.get(entry), writable)
         return None
 
+    def state_snapshot(self) -> dict:
+        """Copies of every per-request state tensor (for a caller that has to run a step twice)."""
+        return {e: st.clone() for e, st in self._state.items() if st is not None}
+
+    def state_restore(self, saved: dict) -> None:
+        for e, st in saved.items():
+            self._state[e].copy_(st)
+
     def group_of(self, entry: int) -> int | None:
         ge = self._entry_group.get(entry)
         return ge[0] if ge else None

@@ -173,6 +173,10 @@ class DecodeGraphs:
             self.graphs[prep["key"]] = slot
         ctx = StepContext(prep["padded"], runner.cache, runner.rt.device, slot["stager"], prep["ex"], prep["plans"])
         ctx.plan_caps = prep["caps"]
+        if prep["key"][0] == "general":
+            # a graph of a padded mixed step is replayed for other steps of its shape: no kernel in it may rest on
+            # every request bringing one token, even if the step it is recorded from happens to be such a step
+            ctx.single_token_step = False
         runner.last_upload_bytes = slot["stager"].bytes_last_upload
         runner.last_context = ctx
         if slot["graph"] is None:
@@ -203,9 +207,11 @@ class DecodeGraphs:
         # so the last-token table is put back afterwards.  Writes to the cache are the same ones the
         # replay makes again.
         saved = last.clone()
+        saved_state = runner.cache.state_snapshot()  # per-request state (a recurrence's, a convolution's) moves only once a step
         torch.cuda.synchronize()
         body()
         last.copy_(saved)
+        runner.cache.state_restore(saved_state)
         torch.cuda.synchronize()
         before = ops.LAUNCHES
         g = torch.cuda.CUDAGraph()
