@@ -278,11 +278,17 @@ def test_latent_rows_are_normed_rotated_and_paged(ops, dtype):
     heads, dim = 3, 8
     q = torch.randn(T, heads * (dim + rot), generator=g).to(DT[dtype])
     qd = q.to(DEV)
-    ops.rotate_pairs(qd, heads, dim + rot, dim, rot_dims, inv.to(DEV), i32(pos), i32(tseq), rank)
+    ops.rotate_pairs(qd, heads, dim + rot, dim, rot, rot_dims, inv.to(DEV), i32(pos), i32(tseq), rank)
     q3 = q.double().view(T, heads, dim + rot)
     want = q3.clone()
     want[..., dim:] = plain.rotate_interleaved(q3[..., dim:], torch.tensor(pos), base, rot_dims)
     assert rel_err(qd.float().cpu().view(T, heads, dim + rot), want) < TOL[dtype]
+    # the same into the tail of wider rows (the layout the tensor-core attention reads)
+    wide = torch.zeros(T, heads * (rank + rot), dtype=DT[dtype], device=DEV)
+    ops.rotate_pairs(q.to(DEV), heads, dim + rot, dim, rot, rot_dims, inv.to(DEV), i32(pos), i32(tseq), rank,
+                     out=wide, out_head_stride=rank + rot, out_off=rank)
+    assert rel_err(wide.float().cpu().view(T, heads, rank + rot)[..., rank:], want[..., dim:]) < TOL[dtype]
+    assert float(wide.view(T, heads, rank + rot)[..., :rank].abs().max()) == 0.0
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -324,6 +330,35 @@ def test_routed_experts_kernels(ops, dtype, E, top, T):
     out = torch.empty(T, W, dtype=DT[dtype], device=DEV)
     ops.moe_combine(y, place, wts, None, out)
     assert rel_err(out.float().cpu(), want) < TOL[dtype]
+
+
+@pytest.mark.parametrize("E,top,T,shared", [(5, 2, 700, True), (3, 1, 1100, False), (9, 3, 260, True)])
+def test_routed_experts_on_the_tensor_cores(ops, E, top, T, shared):
+    """The part itself in bfloat16 with enough rows for the gathered tcgen05 products (spans of 128-row tiles, one
+    expert's weights a tile), against the plain statement; inner size and width are no multiples of the tiles."""
+    from tokasaurus_b200.engine.runtime import Runtime
+    from tokasaurus_b200.parts import GatedMLP, RoutedExperts
+
+    W, F = 136, 88
+    g = torch.Generator().manual_seed(E + T)
+    p = {"router": torch.randn(E, W, generator=g), "router.b": torch.randn(E, generator=g)}
+    for e in range(E):
+        for n, shape in (("gate", (F, W)), ("up", (F, W)), ("down", (W, F))):
+            p[f"e{e}.{n}"] = (torch.randn(shape, generator=g) * 0.2).to(torch.bfloat16)
+    if shared:
+        for n, shape in (("gate", (48, W)), ("up", (48, W)), ("down", (W, 48))):
+            p[f"shared.{n}"] = (torch.randn(shape, generator=g) * 0.2).to(torch.bfloat16)
+    part = RoutedExperts(W, F, E, top, "router", "router.b", lambda e: (f"e{e}.gate", f"e{e}.up", f"e{e}.down"),
+                         GatedMLP(W, 48, "shared.gate", "shared.up", "shared.down") if shared else None)
+    assert T * top >= part.TENSOR_CORE_PAIRS_MIN
+    part.bind({k: v.to(DEV) for k, v in p.items()}, Runtime.make(DEV, "bfloat16"))
+    assert part.w_gate_up_tc is not None
+    h = torch.randn(T, W, generator=g).to(torch.bfloat16)
+    got = part.forward(None, h.to(DEV))
+    if got.dim() == 3:
+        got = got.sum(0)
+    want = plain.routed_ff(h.double(), {k: v.double() for k, v in p.items()}, E, top, shared)
+    assert rel_err(got.float().cpu(), want) < TOL["bfloat16"]
 
 
 # ------------------------------------------------------------------------------------------------ whole models
@@ -463,15 +498,31 @@ def test_cuttings_match_plain(models, which, cut, dtype):
         assert any(len(v) > 1 for v in slots.values()), "no slot was used by two requests"
 
 
+def test_cuttings_with_the_tensor_core_expert_products(models, monkeypatch):
+    """The same in bfloat16 with the gathered tcgen05 expert products used from 24 (token, choice) pairs on, so that
+    portions of prompts go through them and single tokens beside them do not."""
+    from tokasaurus_b200.engine.trace import TraceReplayer
+    from tokasaurus_b200.parts import RoutedExperts
+
+    monkeypatch.setattr(RoutedExperts, "TENSOR_CORE_PAIRS_MIN", 24)
+    for which in MODELS:
+        m = models[which]
+        for cut in ("whole", "mixed"):
+            steps = CUTS[cut](m["reqs"])
+            rp = TraceReplayer(str(m["folder"]), "bfloat16", pool_tokens(steps, m["config"], m["page"]), page_size=m["page"],
+                               max_requests=4)
+            check_logits(cuttings.collect(steps, [rp.run_step(st) for st in steps]), m, "bfloat16", cut)
+
+
 def test_windows_taps_and_state_show_in_the_logits(models):
     """The comparisons above would not notice a window off by one, a lost tap or a state that is not carried if those
-    carried no weight: on the plain implementation, changing each moves the logits by a thousand times the tolerance
+    carried no weight: on the plain implementation, changing each moves the logits by hundreds of times the tolerance
     of the float32 comparisons (the bfloat16 ones are coarser; for them the edges of a window are shown with a made-up
     key in ``test_latent_attention_window_edges``)."""
     m = models["a"]
     rid, toks = max(m["reqs"].items(), key=lambda kv: len(kv[1]))
     ref = m["want"][rid]
-    tol = 1e-2 * float(np.sqrt((ref ** 2).mean()))  # the float32 comparisons allow 3e-5 of the same scale
+    tol = 1e-3 * float(np.sqrt((ref ** 2).mean()))  # a hundred times what the float32 comparisons allow, taken three times below
 
     def moved(config, weights=None):
         d = plain.forward(config, weights or m["weights"], toks).numpy() - ref

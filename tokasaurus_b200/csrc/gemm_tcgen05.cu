@@ -40,7 +40,8 @@ template <int BN> struct Cfg {
 template <int BN, bool GATED>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    bf16* __restrict__ out, int ldo, int M, int N, int K, int* __restrict__ status) {
+                    bf16* __restrict__ out, int ldo, int M, int N, int K, int* __restrict__ status,
+                    const int* __restrict__ tile_group, int group_rows) {
   extern __shared__ unsigned char smem_raw[];
   constexpr int STAGES = Cfg<BN>::STAGES;
   __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
@@ -80,7 +81,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       uint32_t it = 0;  // k-blocks issued so far, over all tiles
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
+        const int m0 = (t % m_tiles) * BM;
+        int n0 = (t / m_tiles) * BN;
+        if (tile_group != nullptr) {
+          // grouped: this row tile multiplies the weights of its own group, group_rows rows further down in W
+          const int g = tile_group[t % m_tiles];
+          if (g < 0) continue;
+          n0 += g * group_rows;
+        }
         for (int kb = 0; kb < n_kblocks; kb++, it++) {
           const int s = it % STAGES;
           if (it >= STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1)) { failed = 1; ok = false; break; }
@@ -97,7 +105,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       constexpr uint32_t idesc = make_idesc(BM, BN);
       uint32_t it = 0, j = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, j++) {
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        if (tile_group != nullptr && tile_group[t % m_tiles] < 0) continue;  // a row tile no group owns
         const uint32_t buf = j & 1;
         if (j >= 2 && !mbar_wait(&acc_empty[buf], ((j >> 1) - 1) & 1)) { failed = 1; ok = false; break; }
         tcgen05_fence_after();
@@ -117,6 +126,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           tcgen05_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
         }
         tcgen05_commit(&acc_full[buf]);  // this tile's accumulator is complete when the MMAs above are
+        j++;
       }
     }
   } else {
@@ -124,7 +134,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int q = warp & 3;
     uint32_t j = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, j++) {
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      if (tile_group != nullptr && tile_group[t % m_tiles] < 0) continue;
       const uint32_t buf = j & 1;
       const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
       if (!mbar_wait(&acc_full[buf], (j >> 1) & 1)) { failed = 1; ok = false; break; }
@@ -182,6 +193,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      j++;
     }
     tcgen05_fence_before();
   }
@@ -195,7 +207,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 template <int BN, bool GATED>
 int launch(const void* A, int lda, const void* W, int ldw, void* out, int ldo, int M, int N, int K, int* status,
-           cudaStream_t st) {
+           cudaStream_t st, const int* tile_group = nullptr, int groups = 1) {
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -206,12 +218,13 @@ int launch(const void* A, int lda, const void* W, int ldw, void* out, int ldo, i
   CUtensorMap map_a, map_w;
   int rc = make_map(&map_a, A, M, K, lda, BM);
   if (rc) return rc;
-  rc = make_map(&map_w, W, N, K, ldw, BN);
+  rc = make_map(&map_w, W, N * groups, K, ldw, BN);
   if (rc) return rc;
   const int n_sms = tkb::sm_count();
   const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
   dim3 grid(tiles < n_sms ? tiles : n_sms);
-  gemm_tcgen05_kernel<BN, GATED><<<grid, THREADS, Cfg<BN>::SMEM_BYTES, st>>>(map_a, map_w, (bf16*)out, ldo, M, N, K, status);
+  gemm_tcgen05_kernel<BN, GATED><<<grid, THREADS, Cfg<BN>::SMEM_BYTES, st>>>(map_a, map_w, (bf16*)out, ldo, M, N, K, status,
+                                                                                 tile_group, N);
   return launch_status();
 }
 
@@ -234,4 +247,24 @@ TKB_EXPORT int tkb_gemm_tcgen05_bf16(const void* A, int lda, const void* W, int 
   }
   return gated ? launch<128, true>(A, lda, W, ldw, out, ldo, M, N, K, status, st)
                : launch<128, false>(A, lda, W, ldw, out, ldo, M, N, K, status, st);
+}
+
+// Grouped form: W is [groups * N, K], rows g * N .. (g + 1) * N the weights of group g, and row tile i of A (128
+// rows) multiplies the weights of group tile_group[i] (a device array of ceil(M / 128) entries; -1: the tile is
+// nobody's and is left out).  The caller orders A's rows by group and starts every group on a tile boundary.
+TKB_EXPORT int tkb_gemm_tcgen05_grouped_bf16(const void* A, int lda, const void* W, int ldw, void* out, int ldo, int M,
+                                             int N, int K, int gated, const int* tile_group, int groups, int* status,
+                                             void* st_) {
+  cudaStream_t st = (cudaStream_t)st_;
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K & 7) || (lda & 7) || (ldw & 7) || (((uintptr_t)A) & 15) || (((uintptr_t)W) & 15)) return -2;
+  if (groups <= 0 || tile_group == nullptr || (gated && (N & 15))) return -2;
+  int rc = get_encode();
+  if (rc) return rc;
+  if (N >= 256) {
+    return gated ? launch<256, true>(A, lda, W, ldw, out, ldo, M, N, K, status, st, tile_group, groups)
+                 : launch<256, false>(A, lda, W, ldw, out, ldo, M, N, K, status, st, tile_group, groups);
+  }
+  return gated ? launch<128, true>(A, lda, W, ldw, out, ldo, M, N, K, status, st, tile_group, groups)
+               : launch<128, false>(A, lda, W, ldw, out, ldo, M, N, K, status, st, tile_group, groups);
 }

@@ -77,25 +77,32 @@ __global__ void latent_prep_kernel(const float* __restrict__ proj, int stride, i
   for (int i = rot_dims + threadIdx.x; i < rot; i += blockDim.x) dst[RANK + i] = from_float<T>(kr[i]);
 }
 
-// In place: the pairs (2i, 2i+1), i < rot_dims / 2, of x[t][head][off ...] are turned by position * inv_freq[i].
+// dst[t][head][dst_off + i] = rotated src[t][head][src_off + i], i < rot: the pairs (2i, 2i+1), i < rot_dims / 2, are
+// turned by position * inv_freq[i], the values from rot_dims on pass unchanged.  dst may be src (in place).
 template <typename T>
-__global__ void rotate_pairs_kernel(T* __restrict__ x, int token_stride, int head_stride, int off, int n_heads,
-                                    int rot_dims, const float* __restrict__ inv_freq,
+__global__ void rotate_pairs_kernel(const T* __restrict__ src, int src_token_stride, int src_head_stride, int src_off,
+                                    T* __restrict__ dst, int dst_token_stride, int dst_head_stride, int dst_off,
+                                    int n_heads, int rot, int rot_dims, const float* __restrict__ inv_freq,
                                     const int* __restrict__ positions, const int* __restrict__ token_seq) {
   trigger_dependents();
   grid_dependency_wait();
   const int t = blockIdx.x;
   if (token_seq[t] < 0) return;
   const float p = (float)positions[t];
-  const int half = rot_dims / 2;
-  for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
-    const int h = idx / half, i = idx - h * half;
-    T* q = x + (size_t)t * token_stride + (size_t)h * head_stride + off;
-    float sn, cs;
-    sincosf(p * inv_freq[i], &sn, &cs);
-    const float u = to_float(q[2 * i]), v = to_float(q[2 * i + 1]);
-    q[2 * i] = from_float<T>(u * cs - v * sn);
-    q[2 * i + 1] = from_float<T>(v * cs + u * sn);
+  const int half = rot_dims / 2, per_head = half + (rot - rot_dims);
+  for (int idx = threadIdx.x; idx < n_heads * per_head; idx += blockDim.x) {
+    const int h = idx / per_head, i = idx - h * per_head;
+    const T* q = src + (size_t)t * src_token_stride + (size_t)h * src_head_stride + src_off;
+    T* o = dst + (size_t)t * dst_token_stride + (size_t)h * dst_head_stride + dst_off;
+    if (i < half) {
+      float sn, cs;
+      sincosf(p * inv_freq[i], &sn, &cs);
+      const float u = to_float(q[2 * i]), v = to_float(q[2 * i + 1]);
+      o[2 * i] = from_float<T>(u * cs - v * sn);
+      o[2 * i + 1] = from_float<T>(v * cs + u * sn);
+    } else {
+      o[rot_dims + i - half] = q[rot_dims + i - half];
+    }
   }
 }
 
@@ -233,12 +240,13 @@ int prep_launch(const float* proj, int stride, int q_off, int q_rank, const floa
 }
 
 template <typename T>
-int rotate_launch(void* x, int token_stride, int head_stride, int off, int n_heads, int rot_dims,
-                  const float* inv_freq, const int* positions, const int* token_seq, int n_tokens, cudaStream_t st) {
-  if (n_tokens <= 0 || rot_dims <= 0) return 0;
-  if (rot_dims % 2) return -2;
-  return launch_pdl(rotate_pairs_kernel<T>, dim3(n_tokens), dim3(128), 0, st, (T*)x, token_stride, head_stride, off,
-                    n_heads, rot_dims, inv_freq, positions, token_seq);
+int rotate_launch(const void* src, int src_ts, int src_hs, int src_off, void* dst, int dst_ts, int dst_hs, int dst_off,
+                  int n_heads, int rot, int rot_dims, const float* inv_freq, const int* positions, const int* token_seq,
+                  int n_tokens, cudaStream_t st) {
+  if (n_tokens <= 0 || rot <= 0) return 0;
+  if (rot_dims % 2 || rot_dims > rot) return -2;
+  return launch_pdl(rotate_pairs_kernel<T>, dim3(n_tokens), dim3(128), 0, st, (const T*)src, src_ts, src_hs, src_off,
+                    (T*)dst, dst_ts, dst_hs, dst_off, n_heads, rot, rot_dims, inv_freq, positions, token_seq);
 }
 
 template <typename T>
@@ -272,11 +280,12 @@ int attn_launch(const void* q_abs, long long qa_ts, long long qa_hs, const void*
                           positions, token_seq, page_indptr, page_ids, page_size, num_pages, eps, n_tokens, status,    \
                           (cudaStream_t)st);                                                                           \
   }                                                                                                                    \
-  TKB_EXPORT int tkb_rotate_pairs_##SUF(void* x, int token_stride, int head_stride, int off, int n_heads,              \
-                                        int rot_dims, const float* inv_freq, const int* positions,                     \
-                                        const int* token_seq, int n_tokens, void* st) {                                \
-    return rotate_launch<T>(x, token_stride, head_stride, off, n_heads, rot_dims, inv_freq, positions, token_seq,      \
-                            n_tokens, (cudaStream_t)st);                                                               \
+  TKB_EXPORT int tkb_rotate_pairs_##SUF(const void* src, int src_ts, int src_hs, int src_off, void* dst, int dst_ts,    \
+                                        int dst_hs, int dst_off, int n_heads, int rot, int rot_dims,                   \
+                                        const float* inv_freq, const int* positions, const int* token_seq,             \
+                                        int n_tokens, void* st) {                                                      \
+    return rotate_launch<T>(src, src_ts, src_hs, src_off, dst, dst_ts, dst_hs, dst_off, n_heads, rot, rot_dims,        \
+                            inv_freq, positions, token_seq, n_tokens, (cudaStream_t)st);                               \
   }                                                                                                                    \
   TKB_EXPORT int tkb_latent_attn_simt_##SUF(const void* q_abs, long long qa_ts, long long qa_hs, const void* q_rot,    \
                                             long long qr_ts, long long qr_hs, int rot, void* out, const void* cache,   \

@@ -68,15 +68,22 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
   for (int k = lane; k < top; k += 32) top_w[(size_t)t * top + k] *= inv;
 }
 
-// One block: offsets[e] .. offsets[e + 1] is expert e's span of the ordering; order[p] is the (token, choice) pair
-// at place p (token * top + choice), place_of[pair] its place (-1 for a padding token's pairs).
-__global__ void moe_order_kernel(const int* __restrict__ top_idx, int n_pairs, int E, int* __restrict__ offsets,
-                                 int* __restrict__ order, int* __restrict__ place_of) {
-  extern __shared__ int cnt[];  // [E] counts, then [E] cursors
+// One block: offsets[e] .. is expert e's span of the ordering; order[p] is the (token, choice) pair at place p
+// (token * top + choice), place_of[pair] its place (-1 for a padding token's pairs).  pad > 1: every span starts at
+// a multiple of pad (the tensor-core product's row tile), offsets[e + 1] - offsets[e] is then the span with its
+// padding; tile_group[i] (n_tiles entries) names the expert that owns row tile i of pad places, -1 for none; and
+// src_token[p] (cap places) is the token whose row stands at place p, -1 at the padding.
+__global__ void moe_order_kernel(const int* __restrict__ top_idx, int n_pairs, int E, int top, int pad,
+                                 int* __restrict__ offsets, int* __restrict__ order, int* __restrict__ place_of,
+                                 int* __restrict__ tile_group, int n_tiles, int* __restrict__ src_token, int cap) {
+  extern __shared__ int cnt[];  // [E] counts, then [E] cursors, then [E + 1] starts
   int* cursor = cnt + E;
+  int* start = cursor + E;
   trigger_dependents();
   grid_dependency_wait();
   for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  if (src_token != nullptr)
+    for (int p = threadIdx.x; p < cap; p += blockDim.x) src_token[p] = -1;
   __syncthreads();
   for (int a = threadIdx.x; a < n_pairs; a += blockDim.x) {
     const int e = top_idx[a];
@@ -88,21 +95,49 @@ __global__ void moe_order_kernel(const int* __restrict__ top_idx, int n_pairs, i
     for (int e = 0; e < E; e++) {
       offsets[e] = run;
       cursor[e] = run;
-      run += cnt[e];
+      start[e] = run;
+      run += (cnt[e] + pad - 1) / pad * pad;
     }
     offsets[E] = run;
+    start[E] = run;
   }
   __syncthreads();
+  if (tile_group != nullptr) {
+    for (int i = threadIdx.x; i < n_tiles; i += blockDim.x) {
+      int g = -1;
+      for (int e = 0; e < E; e++)
+        if (i * pad >= start[e] && i * pad < start[e] + cnt[e]) g = e;
+      tile_group[i] = g;
+    }
+  }
   for (int a = threadIdx.x; a < n_pairs; a += blockDim.x) {
     const int e = top_idx[a];
     if (e >= 0 && e < E) {
       const int p = atomicAdd(&cursor[e], 1);
       order[p] = a;
       place_of[a] = p;
+      if (src_token != nullptr && p < cap) src_token[p] = a / top;
     } else {
       place_of[a] = -1;
     }
   }
+}
+
+// dst[p] = src[src_token[p]] (zeros where src_token[p] < 0): the step's rows in the order of the experts' spans.
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ src, const int* __restrict__ src_token, T* __restrict__ dst,
+                                  int H) {
+  trigger_dependents();
+  grid_dependency_wait();
+  const int p = blockIdx.x;
+  const int t = src_token[p];
+  T* d = dst + (size_t)p * H;
+  if (t < 0) {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) d[i] = from_float<T>(0.f);
+    return;
+  }
+  const T* r = src + (size_t)t * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) d[i] = r[i];
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -202,8 +237,8 @@ moe_gemm_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ W, TC*
 
 // out[t] = sum_k top_w[t, k] * y[place_of[t * top + k]]  (+ shared[t]), in choice order, float32 sums, rounded once.
 // shared: [rows, H] in the activation type, or float32 slices [n_slices][rows, H] added in slice order.
-template <typename T>
-__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place_of,
+template <typename T, typename TY>
+__global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ place_of,
                                    const float* __restrict__ top_w, const T* __restrict__ shared_t,
                                    const float* __restrict__ shared_slices, int n_slices, long long slice_stride,
                                    T* __restrict__ out, int H, int top) {
@@ -214,7 +249,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     float acc = 0.f;
     for (int k = 0; k < top; k++) {
       const int p = place_of[(size_t)t * top + k];
-      if (p >= 0) acc = fmaf(top_w[(size_t)t * top + k], y[(size_t)p * H + i], acc);
+      if (p >= 0) acc = fmaf(top_w[(size_t)t * top + k], to_float(y[(size_t)p * H + i]), acc);
     }
     if (shared_t != nullptr) acc += to_float(shared_t[(size_t)t * H + i]);
     for (int s = 0; s < n_slices; s++) acc += shared_slices[(size_t)s * slice_stride + (size_t)t * H + i];
@@ -244,22 +279,23 @@ int gemm_launch(const void* A, int lda, const void* W, void* C, int ldc, const i
                     lda, (const TA*)W, (TC*)C, ldc, offsets, order, top, E, N, K);
 }
 
-template <typename T>
-int combine_launch(const float* y, const int* place_of, const float* top_w, const void* shared_t,
+template <typename T, typename TY>
+int combine_launch(const void* y, const int* place_of, const float* top_w, const void* shared_t,
                    const float* shared_slices, int n_slices, long long slice_stride, void* out, int n_tokens, int H,
                    int top, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
-  return launch_pdl(moe_combine_kernel<T>, dim3(n_tokens), dim3(H >= 1024 ? 256 : 128), 0, st, y, place_of, top_w,
+  return launch_pdl(moe_combine_kernel<T, TY>, dim3(n_tokens), dim3(H >= 1024 ? 256 : 128), 0, st, (const TY*)y, place_of, top_w,
                     (const T*)shared_t, shared_slices, n_slices, slice_stride, (T*)out, H, top);
 }
 
 }  // namespace
 
-TKB_EXPORT int tkb_moe_order(const int* top_idx, int n_pairs, int E, int* offsets, int* order, int* place_of, void* st) {
+TKB_EXPORT int tkb_moe_order(const int* top_idx, int n_pairs, int E, int top, int pad, int* offsets, int* order,
+                             int* place_of, int* tile_group, int n_tiles, int* src_token, int cap, void* st) {
   if (n_pairs <= 0) return 0;
-  if (E <= 0 || (size_t)E * 8 > 48 * 1024) return -2;
-  return launch_pdl(moe_order_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), (cudaStream_t)st, top_idx, n_pairs,
-                    E, offsets, order, place_of);
+  if (E <= 0 || top <= 0 || pad <= 0 || (size_t)(3 * E + 1) * 4 > 48 * 1024) return -2;
+  return launch_pdl(moe_order_kernel, dim3(1), dim3(1024), (size_t)(3 * E + 1) * sizeof(int), (cudaStream_t)st, top_idx,
+                    n_pairs, E, top, pad, offsets, order, place_of, tile_group, n_tiles, src_token, cap);
 }
 
 #define TKB_MOE_EXPORTS(SUF, T)                                                                                        \
@@ -278,9 +314,23 @@ TKB_EXPORT int tkb_moe_order(const int* top_idx, int n_pairs, int E, int* offset
   TKB_EXPORT int tkb_moe_combine_##SUF(const float* y, const int* place_of, const float* top_w, const void* shared_t,  \
                                        const float* shared_slices, int n_slices, long long slice_stride, void* out,    \
                                        int n_tokens, int H, int top, void* st) {                                       \
-    return combine_launch<T>(y, place_of, top_w, shared_t, shared_slices, n_slices, slice_stride, out, n_tokens, H,    \
-                             top, (cudaStream_t)st);                                                                   \
+    return combine_launch<T, float>(y, place_of, top_w, shared_t, shared_slices, n_slices, slice_stride, out, n_tokens, \
+                                    H, top, (cudaStream_t)st);                                                         \
+  }                                                                                                                    \
+  TKB_EXPORT int tkb_moe_gather_##SUF(const void* src, const int* src_token, void* dst, int n_places, int H,           \
+                                      void* st) {                                                                      \
+    if (n_places <= 0) return 0;                                                                                       \
+    return launch_pdl(moe_gather_kernel<T>, dim3(n_places), dim3(H >= 1024 ? 256 : 128), 0, (cudaStream_t)st,          \
+                      (const T*)src, src_token, (T*)dst, H);                                                           \
   }
 
 TKB_MOE_EXPORTS(f32, float)
 TKB_MOE_EXPORTS(bf16, __nv_bfloat16)
+
+// The same weighted sum over expert outputs kept in bfloat16 (the tensor-core products' result).
+TKB_EXPORT int tkb_moe_combine_y16_bf16(const void* y, const int* place_of, const float* top_w, const void* shared_t,
+                                        const float* shared_slices, int n_slices, long long slice_stride, void* out,
+                                        int n_tokens, int H, int top, void* st) {
+  return combine_launch<__nv_bfloat16, __nv_bfloat16>(y, place_of, top_w, shared_t, shared_slices, n_slices, slice_stride,
+                                                      out, n_tokens, H, top, (cudaStream_t)st);
+}

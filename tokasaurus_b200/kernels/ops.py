@@ -841,15 +841,25 @@ def latent_prep(proj: torch.Tensor, q_off: int, q_rank: int, q_norm_w: torch.Ten
              _stream()), "latent_prep")
 
 
-def rotate_pairs(x: torch.Tensor, n_heads: int, head_stride: int, off: int, rot_dims: int, inv_freq: torch.Tensor,
-                 positions: torch.Tensor, token_seq: torch.Tensor, rank: int) -> None:
-    """In place: in every head of every row of x [T, .], the pairs (off + 2i, off + 2i + 1), i < rot_dims / 2, are
-    turned by position * inv_freq[i] (interleaved rotary encoding)."""
-    _need_cuda(x, inv_freq, positions, token_seq)
-    _need(x.stride(1) == 1 and off + rot_dims <= head_stride and n_heads * head_stride <= x.shape[1], "rotate_pairs: layout")
-    _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2, "rotate_pairs: inv_freq float32 [rot_dims / 2]")
+def rotate_pairs(x: torch.Tensor, n_heads: int, head_stride: int, off: int, rot: int, rot_dims: int,
+                 inv_freq: torch.Tensor | None, positions: torch.Tensor, token_seq: torch.Tensor, rank: int,
+                 out: torch.Tensor | None = None, out_head_stride: int = 0, out_off: int = 0) -> None:
+    """Interleaved rotary encoding of the ``rot`` values at column ``off`` of every head of x [T, .]: the pairs
+    (2i, 2i + 1), i < rot_dims / 2, are turned by position * inv_freq[i], the rest passes.  In place, or into the
+    columns ``out_off`` of every head of ``out`` [T, .]."""
+    _need_cuda(x, inv_freq, positions, token_seq, out)
+    _need(x.stride(1) == 1 and off + rot <= head_stride and n_heads * head_stride <= x.shape[1], "rotate_pairs: layout")
+    _need(rot_dims == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2),
+          "rotate_pairs: inv_freq float32 [rot_dims / 2]")
+    if out is None:
+        if rot_dims == 0:
+            return
+        out, out_head_stride, out_off = x, head_stride, off
+    _need(out.dtype == x.dtype and out.stride(1) == 1 and out.shape[0] == x.shape[0] and out_off + rot <= out_head_stride
+          and n_heads * out_head_stride <= out.shape[1], "rotate_pairs: out layout")
     f = _fn(_libs.get("latent_attention.cu", TKB_LAT_RANK=rank), f"tkb_rotate_pairs_{_suffix(x.dtype)}")
-    _check(f(_ptr(x), c_int(x.stride(0)), c_int(head_stride), c_int(off), c_int(n_heads), c_int(rot_dims), _ptr(inv_freq),
+    _check(f(_ptr(x), c_int(x.stride(0)), c_int(head_stride), c_int(off), _ptr(out), c_int(out.stride(0)),
+             c_int(out_head_stride), c_int(out_off), c_int(n_heads), c_int(rot), c_int(rot_dims), _ptr(inv_freq),
              _ptr(positions), _ptr(token_seq), c_int(x.shape[0]), _stream()), "rotate_pairs")
 
 
@@ -894,15 +904,55 @@ def moe_route(h: torch.Tensor, router_w: torch.Tensor, router_b: torch.Tensor | 
 
 
 def moe_order(top_idx: torch.Tensor, n_experts: int, offsets: torch.Tensor, order: torch.Tensor,
-              place_of: torch.Tensor) -> None:
-    """Order the (token, choice) pairs by expert: offsets int32 [E + 1], order int32 [pairs] (pair at each place),
-    place_of int32 [pairs] (place of each pair, -1 for pairs of padding tokens)."""
-    _need_cuda(top_idx, offsets, order, place_of)
+              place_of: torch.Tensor, pad: int = 1, tile_group: torch.Tensor | None = None,
+              src_token: torch.Tensor | None = None) -> None:
+    """Order the (token, choice) pairs by expert: offsets int32 [E + 1], order int32 (pair at each place),
+    place_of int32 [pairs] (place of each pair, -1 for pairs of padding tokens).  ``pad`` > 1: every expert's span
+    starts at a multiple of ``pad``; ``tile_group`` int32 [tiles] then receives the expert that owns each tile of
+    ``pad`` places (-1: none) and ``src_token`` int32 [places] the token whose row stands at each place (-1: padding);
+    ``order`` must then hold as many entries as ``src_token``."""
+    _need_cuda(top_idx, offsets, order, place_of, tile_group, src_token)
     n = top_idx.numel()
-    _need(all(t.dtype == torch.int32 and t.is_contiguous() for t in (top_idx, offsets, order, place_of)), "moe_order: int32")
-    _need(offsets.numel() == n_experts + 1 and order.numel() == n and place_of.numel() == n, "moe_order: sizes")
-    _check(_fn(_libs.get("moe.cu"), "tkb_moe_order")(_ptr(top_idx), c_int(n), c_int(n_experts), _ptr(offsets), _ptr(order),
-                                                     _ptr(place_of), _stream()), "moe_order")
+    top = top_idx.shape[1]
+    for t in (top_idx, offsets, order, place_of, tile_group, src_token):
+        _need(t is None or (t.dtype == torch.int32 and t.is_contiguous()), "moe_order: int32 arrays")
+    _need(offsets.numel() == n_experts + 1 and place_of.numel() == n, "moe_order: sizes")
+    cap = n if pad == 1 else (n // pad + n_experts) * pad  # the spans, each rounded up to whole tiles, never take more
+    _need(order.numel() >= cap, "moe_order: room for the padded ordering")
+    if pad > 1:
+        _need(tile_group is not None and src_token is not None and src_token.numel() >= cap
+              and tile_group.numel() * pad >= cap, "moe_order: tile groups and source tokens for the padded ordering")
+    _check(_fn(_libs.get("moe.cu"), "tkb_moe_order")(
+        _ptr(top_idx), c_int(n), c_int(n_experts), c_int(top), c_int(pad), _ptr(offsets), _ptr(order), _ptr(place_of),
+        _ptr(tile_group), c_int(tile_group.numel() if tile_group is not None else 0), _ptr(src_token),
+        c_int(src_token.numel() if src_token is not None else 0), _stream()), "moe_order")
+
+
+def moe_gather(src: torch.Tensor, src_token: torch.Tensor, out: torch.Tensor) -> None:
+    """out[p] = src[src_token[p]], zeros where src_token[p] < 0."""
+    _need_cuda(src, src_token, out)
+    _need(src.is_contiguous() and out.is_contiguous() and out.dtype == src.dtype and out.shape[1] == src.shape[1]
+          and src_token.dtype == torch.int32 and src_token.numel() == out.shape[0], "moe_gather: shapes")
+    f = _fn(_libs.get("moe.cu"), f"tkb_moe_gather_{_suffix(src.dtype)}")
+    _check(f(_ptr(src), _ptr(src_token), _ptr(out), c_int(out.shape[0]), c_int(src.shape[1]), _stream()), "moe_gather")
+
+
+def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, status: torch.Tensor,
+                         gated: bool = False) -> torch.Tensor:
+    """Row tile i (128 rows) of a[M, K] times the weights w[tile_group[i]] of w [groups, N, K], bfloat16 on the tcgen05
+    tensor cores; tiles with tile_group[i] < 0 are left out (their rows of the result are not written).
+    ``gated``: every group's rows interleave gate and up (``interleave_gate_up``); the result is [M, N / 2]."""
+    _need_cuda(a, w, tile_group, status)
+    G, N, K = w.shape
+    _need(can_use_tcgen05(a, w.view(G * N, K)) and a.shape[1] == K, "gemm_tcgen05_grouped: bfloat16, K a multiple of 8")
+    M = a.shape[0]
+    _need(tile_group.dtype == torch.int32 and tile_group.numel() * 128 >= M, "gemm_tcgen05_grouped: a group for every row tile")
+    _need(not gated or N % 16 == 0, "gemm_tcgen05_grouped: gated rows come in groups of 16")
+    out = torch.empty((M, N // 2 if gated else N), dtype=torch.bfloat16, device=a.device)
+    _check(_fn(_libs.get("gemm_tcgen05.cu"), "tkb_gemm_tcgen05_grouped_bf16")(
+        _ptr(a), c_int(a.stride(0)), _ptr(w), c_int(K), _ptr(out), c_int(out.stride(0)), c_int(M), c_int(N), c_int(K),
+        c_int(1 if gated else 0), _ptr(tile_group), c_int(G), _ptr(status), _stream()), "gemm_tcgen05_grouped")
+    return out
 
 
 def moe_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor | None,
@@ -928,9 +978,11 @@ def moe_combine(y: torch.Tensor, place_of: torch.Tensor, top_w: torch.Tensor, sh
     _need_cuda(y, place_of, top_w, shared, out)
     T, H = out.shape
     top = top_w.shape[1]
-    _need(y.dtype == torch.float32 and y.is_contiguous() and y.shape[1] == H and out.is_contiguous(), "moe_combine: y, out")
+    _need(y.is_contiguous() and y.shape[1] == H and out.is_contiguous(), "moe_combine: y, out")
+    _need(y.dtype == torch.float32 or (y.dtype == torch.bfloat16 and out.dtype == torch.bfloat16),
+          "moe_combine: expert outputs float32, or bfloat16 in a bfloat16 engine")
     d, sl, n_sl, stride = _split_update(shared, T, H, out.dtype, "moe_combine")
-    f = _fn(_libs.get("moe.cu"), f"tkb_moe_combine_{_suffix(out.dtype)}")
+    f = _fn(_libs.get("moe.cu"), "tkb_moe_combine_y16_bf16" if y.dtype == torch.bfloat16 else f"tkb_moe_combine_{_suffix(out.dtype)}")
     _check(f(_ptr(y), _ptr(place_of), _ptr(top_w), _ptr(d), _ptr(sl), c_int(n_sl), ctypes.c_longlong(stride), _ptr(out),
              c_int(T), c_int(H), c_int(top), _stream()), "moe_combine")
 

@@ -149,7 +149,68 @@ def plan_attention(host, window: int | None, capacity: dict | None = None, block
                 tiles=padded(tiles, 2 * cap.get("tiles", 0)), **extra)
 
 
-class PagedAttention(Mixer):
+class AttentionPlanning:
+    """The host-side work plans of the tensor-core attention kernels, for any mixer that runs them over a paged
+    cache: it needs ``window``, ``n_heads``, ``n_kv_heads``, ``head_dim`` (the cached row's size), ``dtype``,
+    ``block_slots`` and ``sm_count``.  Mixers with equal plan keys share one plan a step."""
+
+    def plan_key(self):
+        if self.dtype != torch.bfloat16:
+            return None
+        return ("paged_attention", self.window, self._blocks_per_item(), self._query_tile(), self.head_dim)
+
+    def _query_tile(self) -> int:
+        return QUERY_TILE_TC if ops.can_use_attn_prefill_tc(self.head_dim) else QUERY_TILE
+
+    def _blocks_per_item(self) -> int:
+        return self.n_kv_heads * ((self.n_heads // self.n_kv_heads + 15) // 16)
+
+    def plan(self, host, capacity=None):
+        return plan_attention(host, self.window, capacity, self._blocks_per_item(), self._query_tile(),
+                              self.block_slots, self.sm_count // self.n_heads)
+
+    def plan_capacity(self, n_requests: int) -> dict:
+        """The most work items ``plan`` can make for a step of ``n_requests`` single-token requests, whatever
+        their contexts: each request gets at most (its keys // the item size) items, at least one."""
+        wave = max(1, self.block_slots // max(1, self._blocks_per_item()))
+        return dict(items=n_requests + wave + wave // 4 + 1, dec=n_requests, tiles=0)
+
+    def plan_capacity_general(self, n_tokens: int, n_requests: int, n_rows: int, counts) -> dict:
+        """Capacities of every work list for a step of up to ``n_tokens`` tokens in ``n_requests`` requests with
+        ``n_rows`` wanted rows; a list the step does not use at all (``counts`` are the plan's own) gets 0, so that
+        its kernel is not launched."""
+        wave = max(1, self.block_slots // max(1, self._blocks_per_item()))
+        spare = wave + wave // 4 + 1
+        has_dec, has_tiles, has_rows = int(counts[1]) > 0, int(counts[2]) > 0, int(counts[4]) > 0
+        return dict(items=(n_requests + spare) if has_dec else 0, dec=n_requests if has_dec else 0,
+                    tiles=(n_tokens // self._query_tile() + n_requests) if has_tiles else 0,
+                    row_items=(n_rows + spare) if has_rows else 0, rows=n_rows if has_rows else 0)
+
+    def pad_plan(self, plan: dict, capacity: dict) -> dict:
+        """The same plan with its arrays at the fixed sizes of a CUDA graph."""
+        def padded(x, n):
+            a = np.zeros(max(n, x.shape[0], 1), dtype=np.int32)
+            a[: x.shape[0]] = x
+            return a
+
+        out = dict(plan)
+        out["items"] = padded(plan["items"], 3 * capacity.get("items", 0))
+        out["item_entry"] = padded(plan["item_entry"], capacity.get("items", 0))
+        out["dec_seqs"] = padded(plan["dec_seqs"], capacity.get("dec", 0))
+        out["dec_item_start"] = padded(plan["dec_item_start"], capacity.get("dec", 0) + 1)
+        out["tiles"] = padded(plan["tiles"], 2 * capacity.get("tiles", 0))
+        if "row_items" in plan:
+            ri, rows = capacity.get("row_items", 0), capacity.get("rows", 0)
+            out["row_items"] = padded(plan["row_items"], 3 * ri)
+            out["row_item_entry"] = padded(plan["row_item_entry"], ri)
+            out["row_item_start"] = padded(plan["row_item_start"], rows + 1)
+            for name in plan:
+                if name in ("row_token", "row_kv_len", "row_index") or name.startswith("row_indptr_g"):
+                    out[name] = padded(plan[name], rows)
+        return out
+
+
+class PagedAttention(AttentionPlanning, Mixer):
     graph_safe = True
 
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, position: PositionEncoding,
@@ -216,61 +277,6 @@ class PagedAttention(Mixer):
         from tokasaurus_b200.kernels.device import NO_DEVICE
 
         self.sm_count = (getattr(rt, "limits", None) or NO_DEVICE).sm_count
-
-    def plan_key(self):
-        if self.dtype != torch.bfloat16:
-            return None
-        return ("paged_attention", self.window, self._blocks_per_item(), self._query_tile(), self.head_dim)
-
-    def _query_tile(self) -> int:
-        return QUERY_TILE_TC if ops.can_use_attn_prefill_tc(self.head_dim) else QUERY_TILE
-
-    def _blocks_per_item(self) -> int:
-        return self.n_kv_heads * ((self.n_heads // self.n_kv_heads + 15) // 16)
-
-    def plan(self, host, capacity=None):
-        return plan_attention(host, self.window, capacity, self._blocks_per_item(), self._query_tile(),
-                              self.block_slots, self.sm_count // self.n_heads)
-
-    def plan_capacity(self, n_requests: int) -> dict:
-        """The most work items ``plan`` can make for a step of ``n_requests`` single-token requests, whatever
-        their contexts: each request gets at most (its keys // the item size) items, at least one."""
-        wave = max(1, self.block_slots // max(1, self._blocks_per_item()))
-        return dict(items=n_requests + wave + wave // 4 + 1, dec=n_requests, tiles=0)
-
-    def plan_capacity_general(self, n_tokens: int, n_requests: int, n_rows: int, counts) -> dict:
-        """Capacities of every work list for a step of up to ``n_tokens`` tokens in ``n_requests`` requests with
-        ``n_rows`` wanted rows; a list the step does not use at all (``counts`` are the plan's own) gets 0, so that
-        its kernel is not launched."""
-        wave = max(1, self.block_slots // max(1, self._blocks_per_item()))
-        spare = wave + wave // 4 + 1
-        has_dec, has_tiles, has_rows = int(counts[1]) > 0, int(counts[2]) > 0, int(counts[4]) > 0
-        return dict(items=(n_requests + spare) if has_dec else 0, dec=n_requests if has_dec else 0,
-                    tiles=(n_tokens // self._query_tile() + n_requests) if has_tiles else 0,
-                    row_items=(n_rows + spare) if has_rows else 0, rows=n_rows if has_rows else 0)
-
-    def pad_plan(self, plan: dict, capacity: dict) -> dict:
-        """The same plan with its arrays at the fixed sizes of a CUDA graph."""
-        def padded(x, n):
-            a = np.zeros(max(n, x.shape[0], 1), dtype=np.int32)
-            a[: x.shape[0]] = x
-            return a
-
-        out = dict(plan)
-        out["items"] = padded(plan["items"], 3 * capacity.get("items", 0))
-        out["item_entry"] = padded(plan["item_entry"], capacity.get("items", 0))
-        out["dec_seqs"] = padded(plan["dec_seqs"], capacity.get("dec", 0))
-        out["dec_item_start"] = padded(plan["dec_item_start"], capacity.get("dec", 0) + 1)
-        out["tiles"] = padded(plan["tiles"], 2 * capacity.get("tiles", 0))
-        if "row_items" in plan:
-            ri, rows = capacity.get("row_items", 0), capacity.get("rows", 0)
-            out["row_items"] = padded(plan["row_items"], 3 * ri)
-            out["row_item_entry"] = padded(plan["row_item_entry"], ri)
-            out["row_item_start"] = padded(plan["row_item_start"], rows + 1)
-            for name in plan:
-                if name in ("row_token", "row_kv_len", "row_index") or name.startswith("row_indptr_g"):
-                    out[name] = padded(plan[name], rows)
-        return out
 
     # --- one step ---
     def forward(self, ctx, h, cache, out_rows=None):

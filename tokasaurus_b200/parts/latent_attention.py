@@ -18,10 +18,20 @@ from __future__ import annotations
 import torch
 
 from tokasaurus_b200.kernels import ops
+from tokasaurus_b200.parts.attention import QUERY_TILE, AttentionPlanning, decode_block_slots
 from tokasaurus_b200.parts.base import Mixer, PagedCacheNeed, WeightSpec
 
+TENSOR_CORE_ROW_MAX = 256  # the widest cached row the mma.sync attention kernels are built for
 
-class LatentAttention(Mixer):
+
+class LatentAttention(AttentionPlanning, Mixer):
+    """In bfloat16, when the cached row (rank + rot values) is a multiple of 16 values and at most 256, the attention
+    runs on the framework's tensor-core kernels for grouped queries: the rows are at once the keys (all rank + rot
+    values) and the values (the kernel's output beyond the first rank values is not used) of ONE key/value head that
+    every query head reads, single tokens through the split-key kernel and portions through the tiled one, planned
+    on the host like ``PagedAttention``'s.  Otherwise (float32, other sizes, only some rows wanted) the FP32-pipe
+    kernel of csrc/latent_attention.cu serves every token."""
+
     graph_safe = True
 
     def __init__(self, width: int, n_heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, q_rank: int,
@@ -37,6 +47,23 @@ class LatentAttention(Mixer):
         self.window = window
         self.names = dict(names)
         self.own_kv = own_kv
+        # what the planning of the tensor-core kernels reads
+        self.n_kv_heads = 1
+        self.head_dim = kv_rank + rot_dim
+        self.block_slots = decode_block_slots(self.head_dim) if self._rows_fit_tensor_cores() else 0
+        self.sm_count = 0
+        self.dtype = None
+
+    def _rows_fit_tensor_cores(self) -> bool:
+        return self.head_dim % 16 == 0 and self.head_dim <= TENSOR_CORE_ROW_MAX
+
+    def _query_tile(self) -> int:
+        return QUERY_TILE
+
+    def plan_key(self):
+        if self.dtype != torch.bfloat16 or not self._rows_fit_tensor_cores():
+            return None
+        return super().plan_key()
 
     def weight_specs(self):
         n, H = self.names, self.n_heads
@@ -53,6 +80,8 @@ class LatentAttention(Mixer):
 
     def kernel_modules(self, dtype):
         mods = [("latent_attention.cu", {"TKB_LAT_RANK": self.kv_rank})]
+        if dtype == "bfloat16" and self._rows_fit_tensor_cores():
+            mods.append(("attention_mma.cu", {"TKB_HD": self.head_dim}))
         return tuple(mods)
 
     def cache_need(self):
@@ -74,6 +103,12 @@ class LatentAttention(Mixer):
         i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
         self.inv_freq = (self.rot_base ** (-2.0 * i / max(self.rot_dims, 1))).to(torch.float32).to(rt.device)
         self.dtype = rt.dtype
+        limits = getattr(rt, "limits", None)
+        if self._rows_fit_tensor_cores():
+            self.block_slots = decode_block_slots(self.head_dim, limits)
+        from tokasaurus_b200.kernels.device import NO_DEVICE
+
+        self.sm_count = (limits or NO_DEVICE).sm_count
 
     def forward(self, ctx, h, cache, out_rows=None):
         T, H, R, rd, dim = h.shape[0], self.n_heads, self.kv_rank, self.rot_dim, self.dim
@@ -85,9 +120,12 @@ class LatentAttention(Mixer):
                         self.dkv_norm, self.inv_freq, cache.k if write else None, ctx.positions, ctx.token_seq,
                         tables.indptr, tables.page_ids, cache.page_size, self.norm_eps, ctx.status, h.dtype)
         q = ops.linear(cq, self.w_uq)  # [T, H * (dim + rot)]
-        if self.rot_dims:
-            ops.rotate_pairs(q, H, dim + rd, dim, self.rot_dims, self.inv_freq, ctx.positions, ctx.token_seq, R)
         q3 = q.view(T, H, dim + rd)
+        plan = ctx.plans.get(self.plan_key()) if (out_rows is None and self.plan_key() is not None) else None
+        if plan is not None:
+            return self._forward_tensor_cores(ctx, q, q3, cache, tables, plan)
+        if self.rot_dims:
+            ops.rotate_pairs(q, H, dim + rd, dim, rd, self.rot_dims, self.inv_freq, ctx.positions, ctx.token_seq, R)
         q_abs = torch.empty((T, H, R), dtype=h.dtype, device=h.device)
         if h.dtype == torch.float32:
             for hh in range(H):
@@ -98,10 +136,43 @@ class LatentAttention(Mixer):
         o_lat = torch.empty((n_rows, H, R), dtype=h.dtype, device=h.device)
         ops.latent_attn(q_abs, q3[:, :, dim:], o_lat, cache.k, ctx.token_seq, ctx.positions, tables.indptr,
                         tables.page_ids, out_rows, n_rows, cache.page_size, self.scale, self.window, ctx.status)
-        val = torch.empty((n_rows, H, self.vdim), dtype=h.dtype, device=h.device)
-        if h.dtype == torch.float32:
+        return self._values_out(o_lat, n_rows)
+
+    def _values_out(self, o_lat, n_rows):
+        """o_lat [rows, H, rank] (any strides with a unit last one) through W_uv, head by head, and W_o."""
+        H = self.n_heads
+        val = torch.empty((n_rows, H, self.vdim), dtype=o_lat.dtype, device=o_lat.device)
+        if o_lat.dtype == torch.float32:
             for hh in range(H):
                 ops.sgemm_tn(o_lat[:, hh, :], self.w_uv[hh], val[:, hh, :])
         else:
             torch.bmm(o_lat.transpose(0, 1), self.w_uv.transpose(1, 2), out=val.transpose(0, 1))
         return ops.linear(val.view(n_rows, H * self.vdim), self.w_o)
+
+    def _forward_tensor_cores(self, ctx, q, q3, cache, tables, plan):
+        T, H, R, rd, dim = q.shape[0], self.n_heads, self.kv_rank, self.rot_dim, self.dim
+        Dk = R + rd
+        # queries as the kernels read them: head by head [q_abs (rank) | rotated q_rot (rot)]
+        q_lat = torch.empty((T, H, Dk), dtype=q.dtype, device=q.device)
+        torch.bmm(q3[:, :, :dim].transpose(0, 1), self.w_uk, out=q_lat[:, :, :R].transpose(0, 1))
+        ops.rotate_pairs(q, H, dim + rd, dim, rd, self.rot_dims, self.inv_freq, ctx.positions, ctx.token_seq, R,
+                         out=q_lat.view(T, H * Dk), out_head_stride=Dk, out_off=R)
+        q2 = q_lat.view(T, H * Dk)
+        attn = torch.empty((T, H * Dk), dtype=q.dtype, device=q.device)
+        caps = ctx.plan_caps.get(self.plan_key()) if ctx.plan_caps else None
+        counts = ctx.host_plans[self.plan_key()]["counts"]
+        items_cap = caps["items"] if caps else int(counts[0])
+        dec_cap = caps["dec"] if caps else int(counts[1])
+        tiles_cap = caps["tiles"] if caps else int(counts[2])
+        c = plan["counts"]
+        rows = cache.k  # keys and values at once
+        if dec_cap:
+            ops.attn_decode_mma(q2, rows, rows, ctx.seq_q_start, ctx.seq_kv_len, tables.indptr, tables.page_ids,
+                                plan["items"], c[0:1], items_cap, plan["dec_seqs"], plan["dec_item_start"], c[1:2],
+                                dec_cap, attn, H, 1, Dk, cache.page_size, self.scale, self.window,
+                                item_entry=plan["item_entry"], tma=bool(counts[5]), status=ctx.status)
+        if tiles_cap:
+            ops.attn_prefill_mma(q2, attn, rows, rows, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, tables.indptr,
+                                 tables.page_ids, plan["tiles"], c[2:3], tiles_cap, H, 1, Dk, cache.page_size, self.scale,
+                                 self.window, ctx.status)
+        return self._values_out(attn.view(T, H, Dk)[:, :, :R], T)

@@ -98,6 +98,8 @@ class RoutedExperts(FeedForward):
     A step's (token, choice) pairs are ordered by expert on the device, and the experts' products run over that
     ordering with each block looking its expert up; nothing about the routing is read back to the host."""
 
+    TENSOR_CORE_PAIRS_MIN = 512  # (token, choice) pairs from which the gathered tcgen05 products are used (bfloat16)
+
     def __init__(self, width: int, inner: int, n_experts: int, top: int, router_name: str, router_bias_name: str | None,
                  expert_names, shared: FeedForward | None = None):
         """``expert_names(e)`` -> (gate, up, down) tensor names of expert e."""
@@ -120,7 +122,8 @@ class RoutedExperts(FeedForward):
         return tuple(specs)
 
     def kernel_modules(self, dtype):
-        return (("moe.cu", None),) + (tuple(self.shared.kernel_modules(dtype)) if self.shared is not None else ())
+        tc = (("gemm_tcgen05.cu", None),) if dtype == "bfloat16" else ()
+        return (("moe.cu", None),) + tc + (tuple(self.shared.kernel_modules(dtype)) if self.shared is not None else ())
 
     def bind(self, weights, rt) -> None:
         self.router_w = weights[self.router_name].contiguous()
@@ -128,6 +131,12 @@ class RoutedExperts(FeedForward):
         # [E, 2 * inner, width]: each expert's gate rows, then its up rows;  [E, width, inner]
         self.w_gate_up = torch.stack([torch.cat([weights[g], weights[u]], dim=0) for g, u, _ in self.expert_names]).contiguous()
         self.w_down = torch.stack([weights[d] for _, _, d in self.expert_names]).contiguous()
+        # for steps of many rows in bfloat16: the same weights with every expert's gate and up rows interleaved in
+        # groups of 8, the layout whose product the tcgen05 kernel turns into silu(gate) * up in its epilogue
+        self.w_gate_up_tc = None
+        if rt.dtype == torch.bfloat16 and self.inner % 8 == 0 and self.width % 8 == 0:
+            self.w_gate_up_tc = torch.stack([ops.interleave_gate_up(weights[g], weights[u])
+                                             for g, u, _ in self.expert_names]).contiguous()
         if self.shared is not None:
             self.shared.bind(weights, rt)
 
@@ -140,14 +149,30 @@ class RoutedExperts(FeedForward):
         token_seq = ctx.token_seq if (ctx is not None and T == ctx.n_tokens) else None
         ops.moe_route(h, self.router_w, self.router_b, token_seq, top, top_idx, top_w)
         offsets = torch.empty((E + 1,), dtype=torch.int32, device=dev)
-        order = torch.empty((T * top,), dtype=torch.int32, device=dev)
         place_of = torch.empty((T * top,), dtype=torch.int32, device=dev)
+        shared = self.shared.forward(ctx, h) if self.shared is not None else None
+        out = torch.empty((T, self.width), dtype=h.dtype, device=dev)
+        if self.w_gate_up_tc is not None and T * top >= self.TENSOR_CORE_PAIRS_MIN:
+            # many rows: the rows gathered expert by expert, every span on a 128-row tile boundary, and the two
+            # products on the tcgen05 tensor cores, each row tile with its own expert's weights
+            tile = 128
+            n_tiles = (T * top) // tile + E
+            order = torch.empty((n_tiles * tile,), dtype=torch.int32, device=dev)
+            src_token = torch.empty((n_tiles * tile,), dtype=torch.int32, device=dev)
+            tile_group = torch.empty((n_tiles,), dtype=torch.int32, device=dev)
+            ops.moe_order(top_idx, E, offsets, order, place_of, pad=tile, tile_group=tile_group, src_token=src_token)
+            rows = torch.empty((n_tiles * tile, self.width), dtype=h.dtype, device=dev)
+            ops.moe_gather(h, src_token, rows)
+            status = ctx.status if ctx is not None else torch.zeros(1, dtype=torch.int32, device=dev)
+            act = ops.gemm_tcgen05_grouped(rows, self.w_gate_up_tc, tile_group, status, gated=True)
+            y = ops.gemm_tcgen05_grouped(act, self.w_down, tile_group, status)
+            ops.moe_combine(y, place_of, top_w, shared, out)
+            return out
+        order = torch.empty((T * top,), dtype=torch.int32, device=dev)
         ops.moe_order(top_idx, E, offsets, order, place_of)
         act = torch.empty((T * top, self.inner), dtype=h.dtype, device=dev)
         ops.moe_gemm(h, self.w_gate_up, act, offsets, order, top, gated=True)
         y = torch.empty((T * top, self.width), dtype=torch.float32, device=dev)
         ops.moe_gemm(act, self.w_down, y, offsets, None, top, gated=False)
-        shared = self.shared.forward(ctx, h) if self.shared is not None else None
-        out = torch.empty((T, self.width), dtype=h.dtype, device=dev)
         ops.moe_combine(y, place_of, top_w, shared, out)
         return out
