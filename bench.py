@@ -2,6 +2,7 @@
 random weights (the metric and configuration of BASELINE.json's configs[2]).
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 2|3|4]
+    python bench.py --design sozurax        (another workload, see run_design; the default's contract is unchanged)
 
 Prints ONE JSON line.  ``value``: decoded tokens a second at batch 8, each request holding a
 2,048-token prompt in the cache, timed on the device with CUDA events around K decode steps
@@ -159,7 +160,9 @@ def prefill_flops(m: dict, T: int, rows: int = 1) -> float:
     return linear + attention
 
 
-TIMED_OPS = ("embed_gather", "add_rmsnorm", "rope_kv_write", "rope_kv_write_partials", "linear_decode", "linear_smallm",
+TIMED_OPS = ("add_layernorm", "add_layernorm_conv1", "short_conv", "polynorm", "gated_recurrence", "latent_prep",
+             "rotate_pairs", "latent_attn", "moe_route", "moe_order", "moe_gather", "moe_gemm", "moe_combine",
+             "gemm_tcgen05_grouped", "embed_gather", "add_rmsnorm", "rope_kv_write", "rope_kv_write_partials", "linear_decode", "linear_smallm",
              "linear_smallm_gated", "silu_mul", "gather_rows", "attn_decode_mma", "attn_decode_rope_mma", "attn_prefill_mma",
              "attn_prefill_tc", "sample", "gemm_tcgen05", "linear_tc_decode", "linear")
 
@@ -649,6 +652,141 @@ def run_reference(args) -> dict:
     return out
 
 
+def design_configs(name: str) -> dict:
+    """Layer sizes for ``--design sozurax``: two sizes that resemble a real model's layers, each as a Sozurax decoder
+    (a recurrent layer with a dense feed-forward, a latent-attention layer with routed experts, a second recurrent
+    layer, a latent-attention layer that reads the first one's rows) and as the closest existing model, a Llama
+    decoder of the same width, depth, vocabulary and dense feed-forward size."""
+    sizes = dict(
+        w2048=dict(width=2048, heads=16, ff=8192, q_rank=768, experts=16, top=2, expert_ff=1024, shared_ff=2048,
+                   llama_heads=32, llama_kv=8),
+        w4096=dict(width=4096, heads=32, ff=14336, q_rank=1536, experts=32, top=4, expert_ff=1024, shared_ff=2048,
+                   llama_heads=32, llama_kv=8))
+    z = sizes[name]
+    W, H = z["width"], z["heads"]
+    rec = dict(type="hgrn2", mixer=dict(heads=H, dim=128, vdim=128))
+    lat = dict(heads=H, dim=128, rot_dim=64, vdim=128, kv_rank=192, q_rank=z["q_rank"], mask=dict(size=1024),
+               rot=dict(base=10000.0, dims=64), scale=192 ** -0.5)
+    moe = dict(kind="moe", expert=dict(ff=z["expert_ff"]), router=dict(experts=z["experts"], top=z["top"]),
+               shared=dict(ff=z["shared_ff"]))
+    soz = dict(architecture="Sozurax", vocab=32000, width=W, norm=dict(eps=1e-6), embedding=dict(scale=1.0),
+               canon=dict(taps=4),
+               layers=[dict(rec, mlp=dict(kind="dense", ff=z["ff"])), dict(type="latent_attention", mixer=dict(lat), mlp=moe),
+                       dict(rec, mlp=moe), dict(type="latent_attention", mixer=dict(lat, kv_from=1), mlp=moe)])
+    llama = dict(architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=4, hidden_size=W,
+                 num_attention_heads=z["llama_heads"], num_key_value_heads=z["llama_kv"], intermediate_size=z["ff"],
+                 vocab_size=32000, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                 max_position_embeddings=131072)
+    return dict(sozurax=soz, llama=llama)
+
+
+def run_design(args) -> dict:
+    """``--design sozurax``: prefill (one 2,048-token prompt in one step) and decode (batch 8 and 64, prompts of 2,048
+    tokens in the cache) of the Sozurax decoder at two layer sizes beside a Llama decoder of equal size, random weights,
+    bfloat16, with the CUDA-event time of each kind of kernel in one prefill step and one decode step of both."""
+    import numpy as np
+    import torch
+
+    from tokasaurus_b200.engine.batch import StepEntry
+    from tokasaurus_b200.engine.engine import Engine
+    from tokasaurus_b200.kernels import ops
+    from tokasaurus_b200.parts import GatedLinearRecurrence, RoutedExperts
+
+    peaks, peak_src = load_peaks()
+    prompt_len, page_size = 2048, 16
+    out = dict(design="sozurax", dtype="bf16", data="synthetic", peaks=dict(peaks, source=peak_src), sizes={})
+    for size in ("w2048", "w4096"):
+        res = {}
+        for arch, cfg in design_configs(size).items():
+            eng = Engine(config_dict=cfg, random_weights=0, dtype="bfloat16", page_size=page_size,
+                         kv_cache_num_tokens=64 * 2304, max_tokens_per_forward=8192, max_seqs_per_forward=64, device="cuda:0")
+            runner, cache, sampler = eng.runner, eng.runner.cache, eng.sampler
+            g = torch.Generator(device="cuda:0").manual_seed(1)
+            for b in runner.model.blocks:
+                # random weights draw every per-channel vector as ones: give the routers logits that differ and the
+                # forget gates lower bounds below one, so that tokens spread over the experts and states stay bounded
+                if isinstance(b.mixer, GatedLinearRecurrence):
+                    b.mixer.lower.uniform_(0.0, 0.9, generator=g)
+                if isinstance(getattr(b, "ffn", None), RoutedExperts):
+                    b.ffn.router_w.normal_(0.0, 1.0, generator=g)
+            vocab = cfg.get("vocab", cfg.get("vocab_size"))
+            tg = torch.Generator().manual_seed(0)
+
+            def tokens(n):
+                return torch.randint(0, vocab, (n,), generator=tg).tolist()
+
+            def event_ms(fn, reps):
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(reps):
+                    fn()
+                b.record()
+                torch.cuda.synchronize()
+                return a.elapsed_time(b) / reps
+
+            pf = tokens(prompt_len)
+
+            def prefill_once():
+                cache.admit("pf")
+                cache.ensure_capacity("pf", prompt_len)
+                runner.step([StepEntry("pf", pf, 0, [prompt_len - 1])])
+                cache.free("pf")
+
+            for _ in range(3):
+                prefill_once()
+            pf_ms = statistics.median(event_ms(prefill_once, 3) for _ in range(3))
+            point = dict(prefill_ms=round(pf_ms, 3), prefill_tok_s=round(prompt_len / pf_ms * 1e3, 1),
+                         prefill_breakdown_us=kernel_breakdown(ops, torch, prefill_once, reps=3))
+            for batch in (8, 64):
+                ids = [f"d{batch}_{i}" for i in range(batch)]
+                for c in range(0, batch, 4):
+                    entries = []
+                    for rid in ids[c:c + 4]:
+                        cache.admit(rid)
+                        cache.ensure_capacity(rid, prompt_len)
+                        entries.append(StepEntry(rid, tokens(prompt_len), 0, [prompt_len - 1]))
+                    logits = runner.step(entries)
+                    slots = torch.tensor([cache.slot(e.request) for e in entries], dtype=torch.int32, device="cuda:0")
+                    sampler.sample(logits, torch.zeros(len(entries), device="cuda:0"), None, None, slots, cache.last_token)
+                    for e in entries:
+                        cache.release_behind_window(e.request, prompt_len)
+                length = {rid: prompt_len for rid in ids}
+                zeros, keys = np.zeros(batch, dtype=np.float32), np.zeros(batch, dtype=np.int64)
+
+                def one(graphs=True):
+                    entries = []
+                    for rid in ids:
+                        cache.ensure_capacity(rid, length[rid] + 1)
+                        entries.append(StepEntry(rid, None, length[rid], [0]))
+                        length[rid] += 1
+                    extra = dict(temperature=zeros, stream_key=keys, sample_pos=np.asarray([length[r] for r in ids], dtype=np.int32),
+                                 row_slot=np.asarray([cache.slot(r) for r in ids], dtype=np.int32))
+                    if graphs and eng.graphs is not None and eng.graphs.usable(entries):
+                        eng.graphs.run(entries, extra)
+                    else:
+                        logits = runner.step(entries, extra)
+                        ex = runner.last_context.extra
+                        sampler.sample(logits, ex["temperature"], ex["stream_key"], ex["sample_pos"], ex["row_slot"], cache.last_token)
+                    for rid in ids:
+                        cache.release_behind_window(rid, length[rid])
+
+                for _ in range(max(3, args.warmup)):
+                    one()
+                ms = event_ms(one, args.steps)
+                point[f"decode_b{batch}_ms"] = round(ms, 4)
+                point[f"decode_b{batch}_tok_s"] = round(batch / ms * 1e3, 1)
+                point[f"decode_b{batch}_breakdown_us"] = kernel_breakdown(ops, torch, lambda: one(False), reps=3)
+                runner.check_status()
+                for rid in ids:
+                    cache.free(rid)
+            res[arch] = point
+            del eng, runner, cache, sampler
+            torch.cuda.empty_cache()
+        out["sizes"][size] = res
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -664,6 +802,9 @@ def main() -> int:
     ap.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference arm may take")
     ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4],
                     help="2: the headline metric (default); 3 and 4: the further workloads, see run_further")
+    ap.add_argument("--design", default=None, choices=["sozurax"],
+                    help="instead of the headline workload: this design's prefill and decode at two layer sizes beside "
+                         "the Llama decoder of equal size (see run_design)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -671,6 +812,9 @@ def main() -> int:
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":
         print(json.dumps(run_reference(args)))
+        return 0
+    if args.design:
+        print(json.dumps(run_design(args)))
         return 0
     print(json.dumps(run_ours(args) if args.config == 2 else run_further(args)))
     return 0

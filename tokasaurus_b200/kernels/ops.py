@@ -790,10 +790,11 @@ def recurrence_defines(dim: int, vdim: int) -> dict:
 def gated_recurrence(qfv: torch.Tensor, state: torch.Tensor, f_bias: torch.Tensor, low: torch.Tensor,
                      norm_w: torch.Tensor, out: torch.Tensor, seq_slot: torch.Tensor, seq_q_start: torch.Tensor,
                      seq_q_len: torch.Tensor, n_seqs: int, heads: int, dim: int, vdim: int, eps: float,
-                     write_state: bool = True) -> None:
+                     write_state: bool = True, split_heads: bool = True) -> None:
     """The recurrence S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t over each request's tokens, then an
     RMS norm of every head's o.  qfv: float32 [T, heads*dim (q) + heads*dim (f) + heads*vdim (v)] raw projections;
-    state: float32 [slots, heads, vdim, dim] (S transposed); out: [T, heads*vdim]."""
+    state: float32 [slots, heads, vdim, dim] (S transposed); out: [T, heads*vdim].  ``split_heads``: a step with more
+    tokens than requests may spread a head's columns over several blocks (raw outputs through a float32 buffer)."""
     _need_cuda(qfv, state, f_bias, low, norm_w, out, seq_slot, seq_q_start, seq_q_len)
     T = qfv.shape[0]
     _need(qfv.dtype == torch.float32 and qfv.stride(1) == 1 and qfv.shape[1] == heads * (2 * dim + vdim),
@@ -804,9 +805,10 @@ def gated_recurrence(qfv: torch.Tensor, state: torch.Tensor, f_bias: torch.Tenso
         _need(v.dtype == torch.float32 and v.is_contiguous() and v.numel() == n, f"gated_recurrence: {what} float32 [{n}]")
     _need(out.is_contiguous() and tuple(out.shape) == (T, heads * vdim), "gated_recurrence: out [T, heads * vdim]")
     f = _fn(_libs.get("recurrence.cu", **recurrence_defines(dim, vdim)), f"tkb_gated_recurrence_{_suffix(out.dtype)}")
+    raw = torch.empty((T, heads * vdim), dtype=torch.float32, device=qfv.device) if (split_heads and T > n_seqs) else None
     _check(f(_ptr(qfv), c_int(qfv.stride(0)), _ptr(state), _ptr(f_bias), _ptr(low), _ptr(norm_w), _ptr(out),
-             _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), c_int(n_seqs), c_int(heads), c_int(dim), c_int(vdim),
-             c_float(eps), c_int(1 if write_state else 0), _stream()), "gated_recurrence")
+             _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), c_int(n_seqs), c_int(T), c_int(heads), c_int(dim),
+             c_int(vdim), c_float(eps), c_int(1 if write_state else 0), _ptr(raw), _stream()), "gated_recurrence")
 
 
 # ---------------------------------------------------------------------------------------------
