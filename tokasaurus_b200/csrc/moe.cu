@@ -10,51 +10,64 @@ using namespace tkb;
 namespace {
 
 // ------------------------------------------------------------------------------------------------
-// One block a token: logits z_e = h . Wr[e] + b[e] in float32 (Wr float32 [E, H]), four experts at a time a warp
-// (the token's row is read once for the four, four sums run side by side); then one warp takes the `top` largest
-// one after the other (equal logits: the lower expert first); weights = softmax over the chosen logits.
+// Router, first kernel: logits z[t][e] = h[t] . Wr[e] + b[e] in float32 (Wr float32 [E, H]).  Block (x, y): four
+// tokens (one a warp) times four experts; the token's row is read once for the four experts, four sums run side by
+// side, and the four warps of a block read the same weight rows (one trip to the L2 for the four).  Few tokens
+// (decoding) still make tokens x E / 4 warps.
 constexpr int ROUTE_WARPS = 4;
 
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
-moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ br,
-                 const int* __restrict__ token_seq, int* __restrict__ top_idx, float* __restrict__ top_w, int H, int E,
-                 int top) {
-  extern __shared__ float z[];  // [E]
+moe_logits_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ br,
+                  float* __restrict__ z, int n_tokens, int H, int E) {
   trigger_dependents();
   grid_dependency_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t = blockIdx.x;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  const int e0 = blockIdx.y * 4;
+  if (t >= n_tokens) return;
+  const T* hr = h + (size_t)t * H;
+  const float* w0 = wr + (size_t)e0 * H;
+  const float* w1 = wr + (size_t)min(e0 + 1, E - 1) * H;
+  const float* w2 = wr + (size_t)min(e0 + 2, E - 1) * H;
+  const float* w3 = wr + (size_t)min(e0 + 3, E - 1) * H;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll 4
+  for (int i = lane; i < H; i += 32) {
+    const float x = to_float(hr[i]);
+    a0 = fmaf(x, w0[i], a0);
+    a1 = fmaf(x, w1[i], a1);
+    a2 = fmaf(x, w2[i], a2);
+    a3 = fmaf(x, w3[i], a3);
+  }
+  a0 = warp_sum(a0); a1 = warp_sum(a1); a2 = warp_sum(a2); a3 = warp_sum(a3);
+  if (lane == 0) {
+    const float acc[4] = {a0, a1, a2, a3};
+    for (int u = 0; u < 4 && e0 + u < E; u++) z[(size_t)t * E + e0 + u] = acc[u] + (br != nullptr ? br[e0 + u] : 0.f);
+  }
+}
+
+// Router, second kernel: one warp a token takes the `top` largest logits one after the other (equal logits: the
+// lower expert first); weights = softmax over the chosen logits.  Rows of padding tokens choose nothing.
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_choose_kernel(const float* __restrict__ z_all, const int* __restrict__ token_seq, int* __restrict__ top_idx,
+                  float* __restrict__ top_w, int n_tokens, int E, int top) {
+  extern __shared__ float zs[];  // [warps][E]
+  trigger_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  if (t >= n_tokens) return;
   if (token_seq != nullptr && token_seq[t] < 0) {
-    for (int k = threadIdx.x; k < top; k += blockDim.x) {
+    for (int k = lane; k < top; k += 32) {
       top_idx[(size_t)t * top + k] = -1;
       top_w[(size_t)t * top + k] = 0.f;
     }
     return;
   }
-  const T* hr = h + (size_t)t * H;
-  for (int e0 = warp * 4; e0 < E; e0 += ROUTE_WARPS * 4) {
-    const float* w0 = wr + (size_t)e0 * H;
-    const float* w1 = wr + (size_t)min(e0 + 1, E - 1) * H;
-    const float* w2 = wr + (size_t)min(e0 + 2, E - 1) * H;
-    const float* w3 = wr + (size_t)min(e0 + 3, E - 1) * H;
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll 4
-    for (int i = lane; i < H; i += 32) {
-      const float x = to_float(hr[i]);
-      a0 = fmaf(x, w0[i], a0);
-      a1 = fmaf(x, w1[i], a1);
-      a2 = fmaf(x, w2[i], a2);
-      a3 = fmaf(x, w3[i], a3);
-    }
-    a0 = warp_sum(a0); a1 = warp_sum(a1); a2 = warp_sum(a2); a3 = warp_sum(a3);
-    if (lane == 0) {
-      const float acc[4] = {a0, a1, a2, a3};
-      for (int u = 0; u < 4 && e0 + u < E; u++) z[e0 + u] = acc[u] + (br != nullptr ? br[e0 + u] : 0.f);
-    }
-  }
-  __syncthreads();
-  if (warp != 0) return;
+  float* z = zs + (size_t)warp * E;
+  for (int e = lane; e < E; e += 32) z[e] = z_all[(size_t)t * E + e];
+  __syncwarp();
   float first = 0.f, denom = 0.f;
   for (int k = 0; k < top; k++) {
     float best = -FLT_MAX;
@@ -378,11 +391,15 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restri
 
 template <typename T>
 int route_launch(const void* h, const float* wr, const float* br, const int* token_seq, int* top_idx, float* top_w,
-                 int n_tokens, int H, int E, int top, cudaStream_t st) {
+                 float* logits, int n_tokens, int H, int E, int top, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
-  if (E <= 0 || top <= 0 || top > E || (size_t)E * 4 > 48 * 1024) return -2;
-  return launch_pdl(moe_route_kernel<T>, dim3(n_tokens), dim3(ROUTE_WARPS * 32), (size_t)E * sizeof(float), st,
-                    (const T*)h, wr, br, token_seq, top_idx, top_w, H, E, top);
+  if (E <= 0 || top <= 0 || top > E || (size_t)E * 4 * ROUTE_WARPS > 48 * 1024 || (E + 3) / 4 > 65535) return -2;
+  const int tb = (n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS;
+  int rc = launch_pdl(moe_logits_kernel<T>, dim3(tb, (E + 3) / 4), dim3(ROUTE_WARPS * 32), 0, st, (const T*)h, wr, br,
+                      logits, n_tokens, H, E);
+  if (rc != 0) return rc;
+  return launch_pdl(moe_choose_kernel, dim3(tb), dim3(ROUTE_WARPS * 32), (size_t)ROUTE_WARPS * E * sizeof(float), st,
+                    (const float*)logits, token_seq, top_idx, top_w, n_tokens, E, top);
 }
 
 template <typename TA, typename TC, bool GATED>
@@ -422,8 +439,9 @@ TKB_EXPORT int tkb_moe_order(const int* top_idx, int n_pairs, int E, int top, in
 
 #define TKB_MOE_EXPORTS(SUF, T)                                                                                        \
   TKB_EXPORT int tkb_moe_route_##SUF(const void* h, const float* wr, const float* br, const int* token_seq,            \
-                                     int* top_idx, float* top_w, int n_tokens, int H, int E, int top, void* st) {      \
-    return route_launch<T>(h, wr, br, token_seq, top_idx, top_w, n_tokens, H, E, top, (cudaStream_t)st);               \
+                                     int* top_idx, float* top_w, float* logits, int n_tokens, int H, int E, int top,   \
+                                     void* st) {                                                                       \
+    return route_launch<T>(h, wr, br, token_seq, top_idx, top_w, logits, n_tokens, H, E, top, (cudaStream_t)st);       \
   }                                                                                                                    \
   TKB_EXPORT int tkb_moe_gemm_gated_##SUF(const void* A, int lda, const void* W, void* C, int ldc, const int* offsets, \
                                           const int* order, int top, int n_places, int E, int N, int K, void* st) {    \

@@ -7,6 +7,23 @@ using namespace tkb;
 
 namespace {
 
+// four consecutive values of the activation type
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<uint32_t*>(&a);
+  u.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
 // ------------------------------------------------------------------------------------------------
 // x += update (float32, written back), then out = (x - mean) / sqrt(var + eps) * w + b, var = mean((x - mean)^2),
 // rounded once to the activation type.  One block a row; the row stays in shared memory between the passes, so the
@@ -30,7 +47,7 @@ __global__ void add_layernorm_kernel(float* __restrict__ x, const T* __restrict_
                                      const float* __restrict__ slices, int n_slices, long long slice_stride,
                                      const float* __restrict__ w, const float* __restrict__ b, T* __restrict__ out,
                                      float eps, int H) {
-  extern __shared__ float row[];
+  extern __shared__ __align__(16) float row[];
   __shared__ float scratch[33];
   trigger_dependents();
   grid_dependency_wait();
@@ -38,6 +55,39 @@ __global__ void add_layernorm_kernel(float* __restrict__ x, const T* __restrict_
   float* xr = x + base;
   const T* dr = delta != nullptr ? delta + base : nullptr;
   const float* sl = slices != nullptr ? slices + base : nullptr;
+  T* orow = out + base;
+  if ((H & 3) == 0) {
+    // four values a thread and pass
+    float s = 0.f;
+    for (int i = 4 * threadIdx.x; i < H; i += 4 * blockDim.x) {
+      float4 v = load4(xr + i);
+      if (dr != nullptr || n_slices > 0) {
+        float4 d = dr != nullptr ? load4(dr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int p = 0; p < n_slices; p++) {
+          const float4 q = load4(sl + (size_t)p * slice_stride + i);
+          d.x += q.x; d.y += q.y; d.z += q.z; d.w += q.w;
+        }
+        v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+        store4(xr + i, v);
+      }
+      store4(row + i, v);
+      s += (v.x + v.y) + (v.z + v.w);
+    }
+    const float mean = block_sum(s, scratch) / (float)H;
+    float ss = 0.f;
+    for (int i = 4 * threadIdx.x; i < H; i += 4 * blockDim.x) {
+      const float4 v = load4(row + i);
+      const float a = v.x - mean, b2 = v.y - mean, c = v.z - mean, d = v.w - mean;
+      ss += (a * a + b2 * b2) + (c * c + d * d);
+    }
+    const float rstd = rsqrtf(block_sum(ss, scratch) / (float)H + eps);
+    for (int i = 4 * threadIdx.x; i < H; i += 4 * blockDim.x) {
+      const float4 v = load4(row + i), g = load4(w + i), o = load4(b + i);
+      store4(orow + i, make_float4((v.x - mean) * rstd * g.x + o.x, (v.y - mean) * rstd * g.y + o.y,
+                                   (v.z - mean) * rstd * g.z + o.z, (v.w - mean) * rstd * g.w + o.w));
+    }
+    return;
+  }
   float s = 0.f;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     const float v = row_update<T>(xr, dr, sl, n_slices, slice_stride, i);
@@ -51,7 +101,6 @@ __global__ void add_layernorm_kernel(float* __restrict__ x, const T* __restrict_
     ss += d * d;
   }
   const float rstd = rsqrtf(block_sum(ss, scratch) / (float)H + eps);
-  T* orow = out + base;
   for (int i = threadIdx.x; i < H; i += blockDim.x) orow[i] = from_float<T>((row[i] - mean) * rstd * w[i] + b[i]);
 }
 
@@ -72,6 +121,23 @@ __global__ void short_conv_kernel(const T* __restrict__ h, T* __restrict__ out, 
   if (s < 0) return;
   const int i = t - seq_q_start[s];  // index of this token among the request's tokens of this step
   const float* cr = carry + (size_t)seq_slot[s] * (taps - 1) * H;
+  if ((H & 3) == 0) {
+    // four channels a thread
+    for (int c = 4 * threadIdx.x; c < H; c += 4 * blockDim.x) {
+      const float4 own = load4(h + (size_t)t * H + c);
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int j = 0; j < taps; j++) {
+        const int k = i - taps + 1 + j;
+        const float4 v = k >= 0 ? load4(h + (size_t)(t - i + k) * H + c) : load4(cr + (size_t)(taps - 1 + k) * H + c);
+        acc.x = fmaf(w[(size_t)(c + 0) * taps + j], v.x, acc.x);
+        acc.y = fmaf(w[(size_t)(c + 1) * taps + j], v.y, acc.y);
+        acc.z = fmaf(w[(size_t)(c + 2) * taps + j], v.z, acc.z);
+        acc.w = fmaf(w[(size_t)(c + 3) * taps + j], v.w, acc.w);
+      }
+      store4(out + (size_t)t * H + c, make_float4(own.x + acc.x, own.y + acc.y, own.z + acc.z, own.w + acc.w));
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
     const float own = to_float(h[(size_t)t * H + c]);
     float acc = 0.f;
@@ -114,7 +180,7 @@ __global__ void add_layernorm_conv1_kernel(float* __restrict__ x, const T* __res
                                            const float* __restrict__ cw, float* __restrict__ carry,
                                            const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
                                            T* __restrict__ out, float eps, int H, int taps) {
-  extern __shared__ float row[];
+  extern __shared__ __align__(16) float row[];
   __shared__ float scratch[33];
   trigger_dependents();
   grid_dependency_wait();

@@ -901,8 +901,9 @@ def moe_route(h: torch.Tensor, router_w: torch.Tensor, router_b: torch.Tensor | 
     _need(top_idx.dtype == torch.int32 and top_w.dtype == torch.float32 and tuple(top_idx.shape) == (T, top)
           and tuple(top_w.shape) == (T, top) and top_idx.is_contiguous() and top_w.is_contiguous(), "moe_route: outputs [T, top]")
     f = _fn(_libs.get("moe.cu"), f"tkb_moe_route_{_suffix(h.dtype)}")
-    _check(f(_ptr(h), _ptr(router_w), _ptr(router_b), _ptr(token_seq), _ptr(top_idx), _ptr(top_w), c_int(T), c_int(H),
-             c_int(E), c_int(top), _stream()), "moe_route")
+    logits = torch.empty((T, E), dtype=torch.float32, device=h.device)
+    _check(f(_ptr(h), _ptr(router_w), _ptr(router_b), _ptr(token_seq), _ptr(top_idx), _ptr(top_w), _ptr(logits), c_int(T),
+             c_int(H), c_int(E), c_int(top), _stream()), "moe_route")
 
 
 def moe_order(top_idx: torch.Tensor, n_experts: int, offsets: torch.Tensor, order: torch.Tensor,

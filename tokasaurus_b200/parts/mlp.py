@@ -98,7 +98,11 @@ class RoutedExperts(FeedForward):
     A step's (token, choice) pairs are ordered by expert on the device, and the experts' products run over that
     ordering with each block looking its expert up; nothing about the routing is read back to the host."""
 
-    TENSOR_CORE_PAIRS_MIN = 512  # (token, choice) pairs from which the gathered tcgen05 products are used (bfloat16)
+    # (token, choice) pairs from which the gathered tcgen05 products are used (bfloat16).  Below, the few-rows kernel
+    # fetches every chosen expert's weights once as well, but spends one multiply-add a row on every weight it
+    # fetches: measured on B200 it wins up to a few rows an expert (16 pairs over 16 experts), and loses by six to
+    # one at eight rows an expert (128 pairs), where the padded 128-row tiles of the tensor cores cost nothing extra.
+    TENSOR_CORE_PAIRS_MIN = 48
 
     def __init__(self, width: int, inner: int, n_experts: int, top: int, router_name: str, router_bias_name: str | None,
                  expert_names, shared: FeedForward | None = None):
