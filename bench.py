@@ -2,7 +2,7 @@
 random weights (the metric and configuration of BASELINE.json's configs[2]).
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 2|3|4]
-    python bench.py --design sozurax        (another workload, see run_design; the default's contract is unchanged)
+    python bench.py --design sozurax        (another workload, see run_design; the default workload and its output line are unchanged)
 
 Prints ONE JSON line.  ``value``: decoded tokens a second at batch 8, each request holding a
 2,048-token prompt in the cache, timed on the device with CUDA events around K decode steps

@@ -31,6 +31,13 @@ def test_description_follows_the_configuration():
     needs = model.cache_entries()
     assert needs[0] == StateNeed((2, 40, 24), "float32")
     assert needs[1] == PagedCacheNeed(1, 42, 19, planes=1)
+    # a reader with a wider window than the layer whose rows it reads: the entry keeps the wider one, each mixer
+    # masks by its own
+    d2 = base_config()
+    d2["layers"][2]["mixer"]["mask"] = dict(size=33)
+    m2 = arch.build_model(arch.parse_config(d2))
+    assert m2.cache_entries()[1] == PagedCacheNeed(1, 42, 33, planes=1)
+    assert [b.mixer.window for b in m2.blocks[1:]] == [19, 33]
     # two stages in layers with a feed-forward, one in the layer without
     stage_entries = [e for names in model.stage_entries for e in names.values()]
     assert len(stage_entries) == 5 and all(needs[e] == StateNeed((2, 64), "float32") for e in stage_entries)

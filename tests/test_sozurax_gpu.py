@@ -393,14 +393,14 @@ MODELS = {
                                   dict(latent(2, 16, 8, 48, 40, 24, 23, rot_dims=6, kv_from=0), mlp=None),
                                   dict(recurrent(2, 20, 12), mlp=moe(24, 6, 2, shared=56))])),
     # a recurrence first, rows of 42 values (no 16-byte multiple), five taps, a window of one page and one longer than
-    # most requests, three chosen experts
+    # most requests, three chosen experts, a reader of another layer's rows with a wider window than that layer's own
     "b": dict(page=16, lengths=[130, 70, 33, 16, 97],
               config=dict(architecture="Sozurax", vocab=97, width=64, norm=dict(eps=1e-6), embedding=dict(scale=1.0),
                           canon=dict(taps=5),
                           layers=[dict(recurrent(1, 64, 64), mlp=dict(kind="dense", ff=80)),
                                   dict(latent(3, 20, 6, 20, 36, 36, 16, base=500.0), mlp=moe(16, 4, 3, shared=32)),
                                   dict(latent(4, 8, 6, 8, 36, 16, 90, base=500.0), mlp=moe(32, 3, 2)),
-                                  dict(latent(3, 20, 6, 20, 36, 36, 16, base=500.0, kv_from=1), mlp=dict(kind="dense", ff=48))])),
+                                  dict(latent(3, 20, 6, 20, 36, 36, 29, base=500.0, kv_from=1), mlp=dict(kind="dense", ff=48))])),
 }
 
 

@@ -32,13 +32,27 @@ moe_logits_kernel(const T* __restrict__ h, const float* __restrict__ wr, const f
   const float* w2 = wr + (size_t)min(e0 + 2, E - 1) * H;
   const float* w3 = wr + (size_t)min(e0 + 3, E - 1) * H;
   float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  if ((H & 3) == 0 && (((uintptr_t)wr) & 15) == 0) {
+    // sixteen bytes of every weight row a lane and pass
+#pragma unroll 2
+    for (int i = lane * 4; i < H; i += 128) {
+      const float x[4] = {to_float(hr[i]), to_float(hr[i + 1]), to_float(hr[i + 2]), to_float(hr[i + 3])};
+      const float4 v0 = *reinterpret_cast<const float4*>(w0 + i), v1 = *reinterpret_cast<const float4*>(w1 + i);
+      const float4 v2 = *reinterpret_cast<const float4*>(w2 + i), v3 = *reinterpret_cast<const float4*>(w3 + i);
+      a0 = fmaf(x[0], v0.x, fmaf(x[1], v0.y, fmaf(x[2], v0.z, fmaf(x[3], v0.w, a0))));
+      a1 = fmaf(x[0], v1.x, fmaf(x[1], v1.y, fmaf(x[2], v1.z, fmaf(x[3], v1.w, a1))));
+      a2 = fmaf(x[0], v2.x, fmaf(x[1], v2.y, fmaf(x[2], v2.z, fmaf(x[3], v2.w, a2))));
+      a3 = fmaf(x[0], v3.x, fmaf(x[1], v3.y, fmaf(x[2], v3.z, fmaf(x[3], v3.w, a3))));
+    }
+  } else {
 #pragma unroll 4
-  for (int i = lane; i < H; i += 32) {
-    const float x = to_float(hr[i]);
-    a0 = fmaf(x, w0[i], a0);
-    a1 = fmaf(x, w1[i], a1);
-    a2 = fmaf(x, w2[i], a2);
-    a3 = fmaf(x, w3[i], a3);
+    for (int i = lane; i < H; i += 32) {
+      const float x = to_float(hr[i]);
+      a0 = fmaf(x, w0[i], a0);
+      a1 = fmaf(x, w1[i], a1);
+      a2 = fmaf(x, w2[i], a2);
+      a3 = fmaf(x, w3[i], a3);
+    }
   }
   a0 = warp_sum(a0); a1 = warp_sum(a1); a2 = warp_sum(a2); a3 = warp_sum(a3);
   if (lane == 0) {

@@ -204,6 +204,36 @@ __global__ void add_layernorm_conv1_kernel(float* __restrict__ x, const T* __res
   }
   const float rstd = rsqrtf(block_sum(ss, scratch) / (float)H + eps);
   float* cr = carry + (size_t)seq_slot[s] * (taps - 1) * H;
+  if ((H & 3) == 0 && taps <= 8) {
+    // four channels a thread: every load of the thread is under way before the first is used
+    for (int c = 4 * threadIdx.x; c < H; c += 4 * blockDim.x) {
+      const float4 xv = load4(row + c), g = load4(w + c), o = load4(b + c);
+      float4 old[7];
+#pragma unroll
+      for (int j = 0; j < 7; j++)
+        if (j < taps - 1) old[j] = load4(cr + (size_t)j * H + c);
+      // the normalised values as the next kernel sees them: rounded to the activation type
+      float own[4] = {(xv.x - mean) * rstd * g.x + o.x, (xv.y - mean) * rstd * g.y + o.y,
+                      (xv.z - mean) * rstd * g.z + o.z, (xv.w - mean) * rstd * g.w + o.w};
+      float res[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        own[u] = to_float(from_float<T>(own[u]));
+        const float* cwr = cw + (size_t)(c + u) * taps;
+        float acc = cwr[taps - 1] * own[u];
+#pragma unroll
+        for (int j = 0; j < 7; j++)
+          if (j < taps - 1) acc = fmaf(cwr[j], u == 0 ? old[j].x : (u == 1 ? old[j].y : (u == 2 ? old[j].z : old[j].w)), acc);
+        res[u] = own[u] + acc;
+      }
+#pragma unroll
+      for (int j = 1; j < 7; j++)
+        if (j < taps - 1) store4(cr + (size_t)(j - 1) * H + c, old[j]);
+      if (taps > 1) store4(cr + (size_t)(taps - 2) * H + c, make_float4(own[0], own[1], own[2], own[3]));
+      store4(out + base + c, make_float4(res[0], res[1], res[2], res[3]));
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
     // the normalised value as the next kernel sees it: rounded to the activation type
     const float own = to_float(from_float<T>((row[c] - mean) * rstd * w[c] + b[c]));

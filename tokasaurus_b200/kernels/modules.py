@@ -24,6 +24,15 @@ def head_dim_modules(head_dim: int, dtype: str | None = None) -> list[tuple[str,
     return mods
 
 
+def family_modules() -> list[tuple[str, dict | None]]:
+    """Kernel modules of parts that only some model families use (layer norm and short convolution, the gated linear
+    recurrence, attention over cached latents, routed experts), at one set of compile-time sizes each: the build check
+    compiles these; a model compiles the sizes it needs (``Part.kernel_modules``)."""
+    return [("norm_conv.cu", None), ("moe.cu", None), ("recurrence.cu", {"TKB_REC_DPT": 16, "TKB_REC_CPT": 1}),
+            ("recurrence.cu", {"TKB_REC_DPT": 3, "TKB_REC_CPT": 2}), ("latent_attention.cu", {"TKB_LAT_RANK": 192}),
+            ("attention_mma.cu", {"TKB_HD": 256})]
+
+
 def optional_modules(head_dim: int) -> list[tuple[str, dict | None]]:
     """Built by the build check, loaded only by callers that ask for them."""
     return EXTRA + [("attention_decode_static.cu", {"TKB_HD": head_dim})]

@@ -35,6 +35,16 @@ from tokasaurus_b200.parts import (
 def build_sozurax(cfg: SozuraxConfig) -> DecoderModel:
     W, eps = cfg.width, cfg.norm_eps
     blocks, order = [], []
+    # a layer that reads another layer's rows has a window of its own: the entry keeps the widest of its users'
+    keep: dict[int, int | None] = {}
+    for i, layer in enumerate(cfg.layers):
+        if isinstance(layer.mixer, LatentMixerConfig):
+            src = i if layer.mixer.kv_from is None else layer.mixer.kv_from
+            w = layer.mixer.window
+            if src not in keep:
+                keep[src] = w
+            elif keep[src] is not None:
+                keep[src] = None if w is None else max(keep[src], w)
     for i, layer in enumerate(cfg.layers):
         p, m = f"l{i}", layer.mixer
         cache = i
@@ -44,7 +54,7 @@ def build_sozurax(cfg: SozuraxConfig) -> DecoderModel:
                 W, m.heads, m.dim, m.rot_dim, m.vdim, m.kv_rank, m.q_rank, m.scale, m.rot_base, m.rot_dims, eps, m.window,
                 names=dict(dq=f"{p}.mix.dq", dq_norm=f"{p}.mix.dq.norm", uq=f"{p}.mix.uq", dkv=f"{p}.mix.dkv",
                            dkv_norm=f"{p}.mix.dkv.norm", uk=f"{p}.mix.uk", uv=f"{p}.mix.uv", o=f"{p}.mix.o"),
-                own_kv=own)
+                own_kv=own, cache_window=keep[i if own else m.kv_from])
             if not own:
                 cache = m.kv_from
         else:

@@ -36,8 +36,11 @@ class LatentAttention(AttentionPlanning, Mixer):
 
     def __init__(self, width: int, n_heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, q_rank: int,
                  scale: float, rot_base: float, rot_dims: int, norm_eps: float, window: int | None, names: dict,
-                 own_kv: bool = True):
-        """``names``: tensors dq, dq_norm, uq, dkv, dkv_norm (both unused without ``own_kv``), uk, uv, o."""
+                 own_kv: bool = True, cache_window: int | None | str = "same"):
+        """``names``: tensors dq, dq_norm, uq, dkv, dkv_norm (both unused without ``own_kv``), uk, uv, o.
+        ``cache_window``: how many of the latest rows the cache entry must keep (None: all); by default this mixer's
+        own ``window``.  Mixers that read one entry with different windows all name the widest one here, so that the
+        entry has one need and no page comes back while a reader can still see it."""
         if rot_dims > rot_dim or rot_dims % 2:
             raise ValueError(f"rot_dims={rot_dims} must be even and at most rot_dim={rot_dim}")
         self.width, self.n_heads, self.dim, self.rot_dim, self.vdim = width, n_heads, dim, rot_dim, vdim
@@ -45,6 +48,9 @@ class LatentAttention(AttentionPlanning, Mixer):
         self.scale, self.rot_base, self.rot_dims = float(scale), float(rot_base), int(rot_dims)
         self.norm_eps = float(norm_eps)
         self.window = window
+        self.cache_window = window if cache_window == "same" else cache_window
+        if self.cache_window is not None and (window is None or window > self.cache_window):
+            raise ValueError(f"a window of {window} rows cannot be read from a cache entry that keeps {self.cache_window}")
         self.names = dict(names)
         self.own_kv = own_kv
         # what the planning of the tensor-core kernels reads
@@ -85,7 +91,7 @@ class LatentAttention(AttentionPlanning, Mixer):
         return tuple(mods)
 
     def cache_need(self):
-        return PagedCacheNeed(1, self.kv_rank + self.rot_dim, self.window, planes=1)
+        return PagedCacheNeed(1, self.kv_rank + self.rot_dim, self.cache_window, planes=1)
 
     def bind(self, weights, rt) -> None:
         n, H = self.names, self.n_heads

@@ -138,7 +138,8 @@ class RoutedExperts(FeedForward):
         # for steps of many rows in bfloat16: the same weights with every expert's gate and up rows interleaved in
         # groups of 8, the layout whose product the tcgen05 kernel turns into silu(gate) * up in its epilogue
         self.w_gate_up_tc = None
-        if rt.dtype == torch.bfloat16 and self.inner % 8 == 0 and self.width % 8 == 0:
+        # (sizes below one tile of the kernel's TMA boxes stay with the other kernels)
+        if rt.dtype == torch.bfloat16 and self.inner % 8 == 0 and self.width % 8 == 0 and self.inner >= 64 and self.width >= 128:
             self.w_gate_up_tc = torch.stack([ops.interleave_gate_up(weights[g], weights[u])
                                              for g, u, _ in self.expert_names]).contiguous()
         if self.shared is not None:
