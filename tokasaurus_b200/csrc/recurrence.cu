@@ -191,7 +191,13 @@ gated_recurrence_split_kernel(const float* __restrict__ qfv, int row_stride, flo
                               const int* __restrict__ seq_q_len, int heads, int dim, int vdim, int write_state,
                               int cols_per_block, float* __restrict__ raw_out) {
   extern __shared__ __align__(16) float smem[];
-  constexpr int DIMP = LANES * DPT;  // a row of gates in shared memory: dim values, then zeros (no bounds in the walk)
+  // A thread's state values: with DPT a multiple of 4 the DPT consecutive dims lane * DPT ..., so that its gates
+  // come out of shared memory as 16-byte vectors (a quarter of the loads); each thread's stretch of a row is
+  // then SP floats apart, SP / 4 odd, which keeps the eight threads of a column on different banks.  Otherwise dims
+  // lane, lane + 8, ... and plain loads.  A row of gates holds dim values, then zeros (no bounds in the walk).
+  constexpr bool VEC = DPT % 4 == 0;
+  constexpr int SP = VEC ? DPT + (((DPT / 4) % 2 == 0) ? 4 : 0) : DPT;
+  constexpr int DIMP = LANES * SP;
   const int stage_floats = CHUNK * (2 * DIMP + cols_per_block);
   float* os = smem + 2 * stage_floats;  // [CHUNK][cols_per_block]
   trigger_dependents();
@@ -213,7 +219,7 @@ gated_recurrence_split_kernel(const float* __restrict__ qfv, int row_stride, flo
     const int j = col0 + c * cols_per_pass;
 #pragma unroll
     for (int i = 0; i < DPT; i++) {
-      const int d = lane + LANES * i;
+      const int d = VEC ? lane * DPT + i : lane + LANES * i;
       S[c][i] = (j < ncols && d < dim) ? st[(size_t)(col_begin + j) * dim + d] : 0.f;
     }
   }
@@ -229,8 +235,9 @@ gated_recurrence_split_kernel(const float* __restrict__ qfv, int row_stride, flo
     for (int idx = tid; idx < nt * d4; idx += blockDim.x) {
       const int t = idx / d4, k = (idx - t * d4) * 4;
       const size_t row = (size_t)(start + t0 + t) * row_stride;
-      cp_async16(qs + t * DIMP + k, q_src + row + k);
-      cp_async16(fs + t * DIMP + k, f_src + row + k);
+      const int at = VEC ? (k / DPT) * SP + (k % DPT) : k;
+      cp_async16(qs + t * DIMP + at, q_src + row + k);
+      cp_async16(fs + t * DIMP + at, f_src + row + k);
     }
     for (int idx = tid; idx < nt * c4; idx += blockDim.x) {
       const int t = idx / c4, k = (idx - t * c4) * 4;
@@ -239,10 +246,8 @@ gated_recurrence_split_kernel(const float* __restrict__ qfv, int row_stride, flo
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   // beyond dim: f = 0 and q = 0, so such a state entry takes the value v and adds nothing to any sum
-  for (int idx = tid; idx < 2 * 2 * CHUNK * (DIMP - dim); idx += blockDim.x) {
-    const int row = idx / (DIMP - dim), k = idx - row * (DIMP - dim);  // rows: [buffer][q|f][token]
-    smem[(row / (2 * CHUNK)) * stage_floats + (row % (2 * CHUNK)) * DIMP + dim + k] = 0.f;
-  }
+  for (int idx = tid; idx < 2 * stage_floats; idx += blockDim.x) smem[idx] = 0.f;
+  __syncthreads();
   fetch(0, 0);
   int buf = 0;
   for (int t0 = 0; t0 < n; t0 += CHUNK, buf ^= 1) {
@@ -265,11 +270,28 @@ gated_recurrence_split_kernel(const float* __restrict__ qfv, int row_stride, flo
         const int j = col0 + c * cols_per_pass;
         const float v = j < ncols ? vs[t * cols_per_block + j] : 0.f;
         float part[4] = {0.f, 0.f, 0.f, 0.f};
+        if (VEC) {
 #pragma unroll
-        for (int i = 0; i < DPT; i++) {
-          const int d = lane + LANES * i;
-          S[c][i] = fmaf(f[d], S[c][i] - v, v);
-          part[i & 3] = fmaf(S[c][i], q[d], part[i & 3]);
+          for (int i4 = 0; i4 < DPT / 4; i4++) {
+            const float4 f4 = *reinterpret_cast<const float4*>(f + lane * SP + 4 * i4);
+            const float4 q4 = *reinterpret_cast<const float4*>(q + lane * SP + 4 * i4);
+            float* Sc = &S[c][(4 * i4) % DPT];
+            Sc[0] = fmaf(f4.x, Sc[0] - v, v);
+            Sc[1] = fmaf(f4.y, Sc[1] - v, v);
+            Sc[2] = fmaf(f4.z, Sc[2] - v, v);
+            Sc[3] = fmaf(f4.w, Sc[3] - v, v);
+            part[0] = fmaf(Sc[0], q4.x, part[0]);
+            part[1] = fmaf(Sc[1], q4.y, part[1]);
+            part[2] = fmaf(Sc[2], q4.z, part[2]);
+            part[3] = fmaf(Sc[3], q4.w, part[3]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < DPT; i++) {
+            const int d = lane + LANES * i;
+            S[c][i] = fmaf(f[d], S[c][i] - v, v);
+            part[i & 3] = fmaf(S[c][i], q[d], part[i & 3]);
+          }
         }
         float acc = (part[0] + part[1]) + (part[2] + part[3]);
         acc += __shfl_xor_sync(0xffffffffu, acc, 1);
@@ -291,7 +313,7 @@ gated_recurrence_split_kernel(const float* __restrict__ qfv, int row_stride, flo
       const int j = col0 + c * cols_per_pass;
 #pragma unroll
       for (int i = 0; i < DPT; i++) {
-        const int d = lane + LANES * i;
+        const int d = VEC ? lane * DPT + i : lane + LANES * i;
         if (j < ncols && d < dim) st[(size_t)(col_begin + j) * dim + d] = S[c][i];
       }
     }
@@ -347,7 +369,8 @@ int launch(float* qfv, int row_stride, float* state, const float* f_bias, const 
                       row_stride, f_bias, low, heads * dim);
   if (rc != 0) return rc;
   const bool by_16 = dim % 4 == 0 && vdim % 4 == 0 && row_stride % 4 == 0 && (((uintptr_t)qfv) & 15) == 0;
-  const size_t smem_split = (size_t)CHUNK * (2 * (2 * LANES * DPT + cols_per_block) + cols_per_block) * sizeof(float);
+  constexpr int SPLIT_SP = (DPT % 4 == 0) ? DPT + (((DPT / 4) % 2 == 0) ? 4 : 0) : DPT;  // as in the kernel
+  const size_t smem_split = (size_t)CHUNK * (2 * (2 * LANES * SPLIT_SP + cols_per_block) + cols_per_block) * sizeof(float);
   if (by_16 && smem_split <= 200 * 1024 && threads <= SPLIT_THREADS_MAX) {
     if (smem_split > 48 * 1024)
       cudaFuncSetAttribute(gated_recurrence_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_split);
