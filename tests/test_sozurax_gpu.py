@@ -247,6 +247,63 @@ def test_latent_attention_window_edges(ops, dtype, rank, rot, page):
                 assert near_far == sees, (far, p, single, sees)
 
 
+@pytest.mark.parametrize("rank,rot,page,heads", [(40, 8, 8, 3), (128, 16, 16, 6), (176, 16, 16, 20)])
+def test_latent_attention_window_edges_on_the_tensor_cores(ops, rank, rot, page, heads):
+    """The same made-up far row through the tensor-core kernels as the latent mixer calls them in bfloat16: the cached
+    rows as keys and as values of one shared head, single tokens through the split-key kernel and a portion through
+    the tiled kernel, rows of 48, 144 and 192 values, 20 query heads on the one row."""
+    from types import SimpleNamespace
+    from tokasaurus_b200.parts.attention import plan_attention
+
+    window, n, scale, Dk = 37, 150, 0.3, rank + rot
+    g = torch.Generator().manual_seed(rank + 1)
+    probe = torch.randn(Dk, generator=g)
+    probe = probe / probe.norm()
+    n_pages = 24
+    perm = torch.randperm(n_pages, generator=g)[: -(-n // page)].tolist()
+    for far in (page * 3, page * 4 - 1, 77):
+        r = (torch.randn(n, Dk, generator=g) * 0.5).to(torch.bfloat16)
+        r[far] = (probe * 6).to(torch.bfloat16)
+        cache = torch.zeros(n_pages, 1, page, Dk, dtype=torch.bfloat16, device=DEV)
+        for j in range(n):
+            cache[perm[j // page], 0, j % page] = r[j].to(DEV)
+        r64 = r.double()
+        pos = list(range(far + window - 3, min(n, far + window + 3)))
+        T = len(pos)
+        q = (torch.randn(T, heads, Dk, generator=g) * 0.3 + probe * 8).to(torch.bfloat16)
+        q2 = q.view(T, heads * Dk).to(DEV)
+        for single in (False, True):
+            if single:
+                lens_q, lens_kv = [1] * T, [p + 1 for p in pos]
+                indptr, ids = [k * len(perm) for k in range(T + 1)], perm * T
+            else:
+                lens_q, lens_kv, indptr, ids = [T], [pos[-1] + 1], [0, len(perm)], perm
+            host = SimpleNamespace(seq_q_len=np.asarray(lens_q, dtype=np.int32), seq_kv_len=np.asarray(lens_kv, dtype=np.int32))
+            plan = plan_attention(host, window, blocks_per_item=(heads + 15) // 16, query_tile=64)
+            c = i32(plan["counts"])
+            n_items, n_dec, n_tiles = (int(x) for x in plan["counts"][:3])
+            out = torch.zeros(T, heads * Dk, dtype=torch.bfloat16, device=DEV)
+            q_start = list(range(T)) if single else [0]
+            status = torch.zeros(1, dtype=torch.int32, device=DEV)
+            if single:
+                assert n_dec == T and n_tiles == 0
+                ops.attn_decode_mma(q2, cache, cache, i32(q_start), i32(lens_kv), i32(indptr), i32(ids), i32(plan["items"]),
+                                    c[0:1], n_items, i32(plan["dec_seqs"]), i32(plan["dec_item_start"]), c[1:2], n_dec, out,
+                                    heads, 1, Dk, page, scale, window, item_entry=i32(plan["item_entry"]), status=status)
+            else:
+                assert n_tiles >= 1 and n_dec == 0
+                ops.attn_prefill_mma(q2, out, cache, cache, i32(q_start), i32(lens_q), i32(lens_kv), i32(indptr), i32(ids),
+                                     i32(plan["tiles"]), c[2:3], n_tiles, heads, 1, Dk, page, scale, window, status)
+            assert int(status.item()) == 0
+            o = out.view(T, heads, Dk)[:, :, :rank].float().cpu().double()
+            for k, p in enumerate(pos):
+                want = latent_reference(q[k, :, :rank].double(), q[k, :, rank:].double(), r64, p, window, scale)
+                assert rel_err(o[k], want) < TOL["bfloat16"], (far, p, single)
+                sees = p - far < window
+                near_far = float((o[k] - r64[far, :rank]).abs().max()) < 0.05 * float(r64[far, :rank].abs().max())
+                assert near_far == sees, (far, p, single, sees)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_latent_rows_are_normed_rotated_and_paged(ops, dtype):
     """latent_prep + rotate_pairs against the plain norm and interleaved rotation, tokens of two requests at
@@ -383,6 +440,14 @@ def moe(ff, experts, top, shared=None):
 
 
 MODELS = {
+    # twenty query heads on one cached row (two tiles of sixteen in the tensor-core kernels), a window of several
+    # key tiles, prompts longer than it, a reader with a narrower window and another head count
+    "c": dict(page=16, lengths=[300, 150, 40, 210, 33, 64],
+              config=dict(architecture="Sozurax", vocab=113, width=128, norm=dict(eps=1e-6), embedding=dict(scale=2.0),
+                          canon=dict(taps=2),
+                          layers=[dict(latent(20, 16, 16, 16, 48, 32, 200, base=2000.0), mlp=dict(kind="dense", ff=96)),
+                                  dict(recurrent(4, 16, 32), mlp=None),
+                                  dict(latent(17, 8, 16, 24, 48, 40, 130, base=2000.0, kv_from=0), mlp=moe(64, 4, 2, shared=64))])),
     # latent attention first, windows no multiple of the page size, a reader of another layer's rows without a
     # feed-forward, one chosen expert without a shared expert, rotary on fewer values than the rotated part holds
     "a": dict(page=8, lengths=[100, 37, 64, 5, 81, 1, 50],
