@@ -100,9 +100,10 @@ class RoutedExperts(FeedForward):
 
     # (token, choice) pairs from which the gathered tcgen05 products are used (bfloat16).  Below, the few-rows kernel
     # fetches every chosen expert's weights once as well, but spends one multiply-add a row on every weight it
-    # fetches: measured on B200 it wins up to a few rows an expert (16 pairs over 16 experts), and loses by six to
-    # one at eight rows an expert (128 pairs), where the padded 128-row tiles of the tensor cores cost nothing extra.
-    TENSOR_CORE_PAIRS_MIN = 48
+    # fetches.  Measured on B200, the whole part replayed from a graph, 16 experts of 1,024 x 2,048, two chosen:
+    # 2 pairs 36 against 44 us, 8 pairs 62 against 64, 16 pairs 83 against 70, 48 pairs 117 against 80 (32 experts of
+    # 1,024 x 4,096, four chosen: 8 pairs 117 against 118, 16 pairs 179 against 132, 96 pairs 366 against 219).
+    TENSOR_CORE_PAIRS_MIN = 12
 
     def __init__(self, width: int, inner: int, n_experts: int, top: int, router_name: str, router_bias_name: str | None,
                  expert_names, shared: FeedForward | None = None):
