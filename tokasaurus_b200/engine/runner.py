@@ -92,7 +92,7 @@ class ModelRunner:
         self.last_upload_bytes = 0
 
     # ------------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry], extra: dict | None = None) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], extra: dict | None = None, layer_outputs: list | None = None) -> torch.Tensor:
         """Run the tokens of ``entries`` as one batch from the cache and return float32 logits
         [wanted places, vocab] on the device, in the order of the entries and of their ``want``.
         Pages for the new positions must have been given to the requests before.  ``extra``: further
@@ -103,6 +103,8 @@ class ModelRunner:
         ctx = StepContext(host, self.cache, self.rt.device, self.stager, extra, plans)
         self.last_upload_bytes = self.stager.bytes_last_upload
         self.last_context = ctx
+        if layer_outputs is not None:
+            ctx.layer_outputs = layer_outputs  # the model appends the stream after every layer call
         return self.model.forward(ctx)
 
     def check_status(self, code: int | None = None) -> None:

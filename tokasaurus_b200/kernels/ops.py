@@ -990,6 +990,182 @@ def moe_combine(y: torch.Tensor, place_of: torch.Tensor, top_w: torch.Tensor, sh
              c_int(T), c_int(H), c_int(top), _stream()), "moe_combine")
 
 
+# ---------------------------------------------------------------------------------------------
+# Blocks that norm a sublayer's output; sinusoidal positions; clamped gated unit; gated norm in parts (csrc/post_norm.cu)
+def scaled_norm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor | None, mult: float,
+                    eps: float, h_out: torch.Tensor | None = None, bias: torch.Tensor | None = None) -> None:
+    """x += mult * scale * weight * N(y + bias) in place (x, y float32; N divides a row by its root mean square);
+    ``h_out`` (activation type, x's shape) receives the new x."""
+    _need_cuda(x, y, weight, scale, h_out, bias)
+    rows, H = x.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous() and y.dtype == torch.float32 and y.is_contiguous()
+          and y.shape == x.shape, "scaled_norm_add: x and y contiguous float32 of one shape")
+    for v, what in ((weight, "norm weight"), (scale, "scale"), (bias, "bias")):
+        _need(v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == H),
+              f"scaled_norm_add: {what} float32 [H]")
+    _need(weight is not None, "scaled_norm_add: a norm weight")
+    _need(h_out is None or (h_out.shape == x.shape and h_out.is_contiguous()), "scaled_norm_add: h_out of x's shape")
+    suf = _suffix(h_out.dtype) if h_out is not None else "f32"
+    _check(_fn(_libs.get("post_norm.cu"), f"tkb_scaled_norm_add_{suf}")(
+        _ptr(x), _ptr(y), _ptr(bias), _ptr(weight), _ptr(scale), c_float(mult), c_float(eps), _ptr(h_out), c_int(rows),
+        c_int(H), _stream()), "scaled_norm_add")
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x (float32) in out's type."""
+    _need_cuda(x, out)
+    _need(x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and out.shape == x.shape, "cast_rows: shapes")
+    _check(_fn(_libs.get("post_norm.cu"), f"tkb_cast_rows_{_suffix(out.dtype)}")(
+        _ptr(x), _ptr(out), ctypes.c_longlong(x.numel()), _stream()), "cast_rows")
+
+
+def add_sinusoid(x: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor) -> None:
+    """x[t, 2i] += sin(positions[t] * freq[i]), x[t, 2i + 1] += cos(same); x float32, angles float32."""
+    _need_cuda(x, positions, freq)
+    rows, H = x.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "add_sinusoid: x contiguous float32")
+    _need(positions.dtype == torch.int32 and positions.numel() >= rows, "add_sinusoid: positions int32 [T]")
+    _need(freq.dtype == torch.float32 and freq.is_contiguous() and freq.numel() == (H + 1) // 2, "add_sinusoid: float32 [ceil(H / 2)] frequencies")
+    _check(_fn(_libs.get("post_norm.cu"), "tkb_add_sinusoid")(_ptr(x), _ptr(positions), _ptr(freq), c_int(rows), c_int(H),
+                                                              _stream()), "add_sinusoid")
+
+
+def clamped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> None:
+    """out = g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit);
+    gate_up [rows, 2 * inner] = [gate | up] in out's type or float32."""
+    _need_cuda(gate_up, out)
+    rows, two_i = gate_up.shape
+    _need(two_i % 2 == 0 and tuple(out.shape) == (rows, two_i // 2) and gate_up.is_contiguous() and out.is_contiguous(),
+          "clamped_glu: shapes")
+    _need(gate_up.dtype in (torch.float32, out.dtype), "clamped_glu: gate_up float32 or in out's type")
+    name = f"tkb_clamped_glu_{_suffix(gate_up.dtype)}_{_suffix(out.dtype)}"
+    _check(_fn(_libs.get("post_norm.cu"), name)(_ptr(gate_up), _ptr(out), c_int(rows), c_int(two_i // 2), c_float(limit),
+                                                c_float(alpha), _stream()), "clamped_glu")
+
+
+def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, groups: int,
+                     eps: float, gate_first: bool) -> None:
+    """Rows of float32 values, RMS-normed in ``groups`` equal parts and gated: ``gate_first`` False:
+    N(y) * weight * sigmoid(gate); True: N(y * silu(gate)) * weight.  ``y`` and ``gate`` may be column slices of wider
+    float32 tensors."""
+    _need_cuda(y, gate, weight, out)
+    rows, width = y.shape
+    _need(y.dtype == torch.float32 and gate.dtype == torch.float32 and y.stride(1) == 1 and gate.stride(1) == 1
+          and gate.shape == y.shape, "gated_group_norm: float32 values and gates of one shape")
+    _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == width, "gated_group_norm: weight float32 [width]")
+    _need(out.stride(1) == 1 and out.shape == y.shape and groups > 0 and width % groups == 0, "gated_group_norm: out, groups")
+    _check(_fn(_libs.get("post_norm.cu"), f"tkb_gated_group_norm_{_suffix(out.dtype)}")(
+        _ptr(y), c_int(y.stride(0)), _ptr(gate), c_int(gate.stride(0)), _ptr(weight), _ptr(out), c_int(out.stride(0)),
+        c_int(rows), c_int(width), c_int(groups), c_float(eps), c_int(1 if gate_first else 0), _stream()), "gated_group_norm")
+
+
+# ---------------------------------------------------------------------------------------------
+# The recurrence with one decay a head and token (csrc/decay_recurrence.cu)
+def decay_recurrence_defines(dim: int, vdim: int) -> dict:
+    _need(0 < dim <= 256 and 0 < vdim <= 512, f"decay recurrence: heads up to 256 x 512, not {dim} x {vdim}")
+    return dict(TKB_DR_DPT=(dim + 7) // 8, TKB_DR_CPT=(vdim + 127) // 128)
+
+
+def ssm_prep(proj: torch.Tensor, xbc_off: int, channels: int, conv_w: torch.Tensor, conv_b: torch.Tensor | None,
+             state: torch.Tensor, carry_off: int, token_seq: torch.Tensor, seq_slot: torch.Tensor,
+             seq_q_start: torch.Tensor, seq_q_len: torch.Tensor, n_seqs: int, xbc: torch.Tensor, dt_off: int,
+             heads: int, dt_bias: torch.Tensor, a_log: torch.Tensor, dt_dec: torch.Tensor, defines: dict,
+             write_state: bool = True) -> None:
+    """From float32 projections [T, .]: xbc = silu(bias + causal convolution over time) of the ``channels`` columns at
+    ``xbc_off`` (inputs from before the step out of state[slot, carry_off:] = [taps - 1, channels], brought forward
+    afterwards), dt = softplus(proj[:, dt_off + h] + dt_bias[h]) and the decay exp(-exp(a_log[h]) * dt) into
+    dt_dec [T, 2 * heads]."""
+    _need_cuda(proj, conv_w, conv_b, state, token_seq, seq_slot, seq_q_start, seq_q_len, xbc, dt_bias, a_log, dt_dec)
+    T = proj.shape[0]
+    taps = conv_w.shape[1]
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] >= max(xbc_off + channels, dt_off + heads),
+          "ssm_prep: float32 projections")
+    _need(conv_w.dtype == torch.float32 and conv_w.is_contiguous() and conv_w.shape[0] == channels, "ssm_prep: taps float32 [channels, taps]")
+    _need(conv_b is None or (conv_b.dtype == torch.float32 and conv_b.numel() == channels), "ssm_prep: bias float32 [channels]")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous()
+          and state.shape[1] >= carry_off + (taps - 1) * channels, "ssm_prep: state float32 [slots, n]")
+    _need(xbc.dtype == torch.float32 and xbc.is_contiguous() and tuple(xbc.shape) == (T, channels), "ssm_prep: xbc float32 [T, channels]")
+    _need(dt_dec.dtype == torch.float32 and dt_dec.is_contiguous() and tuple(dt_dec.shape) == (T, 2 * heads), "ssm_prep: dt_dec [T, 2 heads]")
+    for v in (dt_bias, a_log):
+        _need(v.dtype == torch.float32 and v.is_contiguous() and v.numel() == heads, "ssm_prep: float32 [heads] vectors")
+    _check(_fn(_libs.get("decay_recurrence.cu", **defines), "tkb_ssm_prep")(
+        _ptr(proj), c_int(proj.stride(0)), c_int(xbc_off), c_int(channels), c_int(taps), _ptr(conv_w), _ptr(conv_b),
+        _ptr(state), ctypes.c_longlong(state.stride(0)), ctypes.c_longlong(carry_off), _ptr(token_seq), _ptr(seq_slot),
+        _ptr(seq_q_start), _ptr(seq_q_len), c_int(T), c_int(n_seqs), _ptr(xbc), c_int(dt_off), c_int(heads),
+        _ptr(dt_bias), _ptr(a_log), _ptr(dt_dec), c_int(1 if write_state else 0), _stream()), "ssm_prep")
+
+
+def decay_walk(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads_per_qk: int, dt_dec: torch.Tensor | None,
+               decay_head: torch.Tensor | None, skip: torch.Tensor | None, state: torch.Tensor, out: torch.Tensor,
+               seq_slot: torch.Tensor, seq_q_start: torch.Tensor, seq_q_len: torch.Tensor, n_seqs: int, heads: int,
+               dim: int, vdim: int, act: bool, defines: dict, write_state: bool = True) -> None:
+    """S_t = a_t S_(t-1) + (c_t k_t) v_t^T, o_t = S_t^T q_t + skip * v_t over each request's tokens.  q, k [T, . * dim]
+    and v [T, heads * vdim] are float32 (column slices allowed); head h reads q and k number h // heads_per_qk;
+    ``act``: all three pass through SiLU.  ``dt_dec`` [T, 2 heads] = (c, a) per token, or ``decay_head`` [heads] with
+    c = 1.  state float32 [slots, n], S^T of the heads first: [heads, vdim, dim]; out float32 [T, heads * vdim]."""
+    _need_cuda(q, k, v, dt_dec, decay_head, skip, state, out, seq_slot, seq_q_start, seq_q_len)
+    T = q.shape[0]
+    for t in (q, k, v):
+        _need(t.dtype == torch.float32 and t.stride(1) == 1 and t.shape[0] == T, "decay_walk: float32 rows")
+    _need(heads_per_qk > 0 and heads % heads_per_qk == 0 and q.shape[1] == (heads // heads_per_qk) * dim
+          and k.shape[1] == q.shape[1] and v.shape[1] == heads * vdim, "decay_walk: shapes of q, k, v")
+    _need((dt_dec is None) != (decay_head is None), "decay_walk: decays per token or per head")
+    _need(dt_dec is None or (dt_dec.dtype == torch.float32 and dt_dec.is_contiguous() and tuple(dt_dec.shape) == (T, 2 * heads)),
+          "decay_walk: dt_dec float32 [T, 2 heads]")
+    for t in (decay_head, skip):
+        _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == heads), "decay_walk: float32 [heads]")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous() and state.shape[1] >= heads * vdim * dim,
+          "decay_walk: state float32 [slots, n]")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape) == (T, heads * vdim), "decay_walk: out float32 [T, heads * vdim]")
+    _check(_fn(_libs.get("decay_recurrence.cu", **defines), "tkb_decay_walk")(
+        _ptr(q), c_int(q.stride(0)), _ptr(k), c_int(k.stride(0)), c_int(heads_per_qk), _ptr(v), c_int(v.stride(0)),
+        _ptr(dt_dec), _ptr(decay_head), _ptr(skip), _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(out),
+        _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), c_int(n_seqs), c_int(T), c_int(heads), c_int(dim), c_int(vdim),
+        c_int(1 if write_state else 0), c_int(1 if act else 0), _stream()), "decay_walk")
+
+
+# ---------------------------------------------------------------------------------------------
+# Attention with a score cap and a sink, keys and values of different sizes (csrc/attention_sink.cu)
+def sink_attention_defines(dim: int, vdim: int) -> dict:
+    _need(0 < dim <= 512 and 0 < vdim <= 512, f"sink attention: head sizes up to 512, not {dim} / {vdim}")
+    return dict(TKB_QK=dim, TKB_VD=vdim)
+
+
+def sink_attn_prep(qkv: torch.Tensor, bias: torch.Tensor | None, unit_norm: bool, eps: float, q_out: torch.Tensor,
+                   cache: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor, page_indptr: torch.Tensor,
+                   page_ids: torch.Tensor, n_heads: int, n_kv_heads: int, dim: int, vdim: int, page_size: int,
+                   write_cache: bool, status: torch.Tensor) -> None:
+    """qkv float32 [T, heads*dim | kv heads*dim | kv heads*vdim] -> (+ bias, q and k heads divided by their root mean
+    square) q_out [T, heads*dim] and the tokens' [k | v] rows in cache [pages, kv heads, page_size, dim + vdim]."""
+    _need_cuda(qkv, bias, q_out, cache, positions, token_seq, page_indptr, page_ids, status)
+    T = qkv.shape[0]
+    C = (n_heads + n_kv_heads) * dim + n_kv_heads * vdim
+    _need(qkv.dtype == torch.float32 and qkv.stride(1) == 1 and qkv.shape[1] == C, "sink_attn_prep: float32 projections")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == C), "sink_attn_prep: bias float32")
+    _need(q_out.is_contiguous() and tuple(q_out.shape) == (T, n_heads * dim) and q_out.dtype == cache.dtype, "sink_attn_prep: q_out")
+    _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (n_kv_heads, page_size, dim + vdim), "sink_attn_prep: cache rows")
+    _check(_fn(_libs.get("attention_sink.cu", **sink_attention_defines(dim, vdim)), f"tkb_sink_attn_prep_{_suffix(cache.dtype)}")(
+        _ptr(qkv), c_int(qkv.stride(0)), _ptr(bias), c_int(1 if unit_norm else 0), c_float(eps), _ptr(q_out), _ptr(cache),
+        _ptr(positions), _ptr(token_seq), _ptr(page_indptr), _ptr(page_ids), c_int(T), c_int(n_heads), c_int(n_kv_heads),
+        c_int(page_size), c_int(cache.shape[0]), c_int(1 if write_cache else 0), _ptr(status), _stream()), "sink_attn_prep")
+
+
+def attn_sink(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
+              page_indptr: torch.Tensor, page_ids: torch.Tensor, rows: torch.Tensor | None, n_rows: int,
+              sinks: torch.Tensor | None, n_heads: int, n_kv_heads: int, dim: int, vdim: int, page_size: int,
+              scale: float, softcap: float | None, window: int | None, status: torch.Tensor) -> None:
+    """Attention of ``n_rows`` tokens (``rows`` names them; None: all) over their requests' cached [k | v] rows."""
+    _need_cuda(q, out, cache, token_seq, positions, page_indptr, page_ids, rows, sinks, status)
+    _need(q.is_contiguous() and q.shape[1] == n_heads * dim and q.dtype == cache.dtype and out.dtype == cache.dtype
+          and out.is_contiguous() and tuple(out.shape) == (n_rows, n_heads * vdim), "attn_sink: q and out")
+    _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (n_kv_heads, page_size, dim + vdim), "attn_sink: cache rows")
+    _need(sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == n_heads), "attn_sink: sinks float32 [heads]")
+    _check(_fn(_libs.get("attention_sink.cu", **sink_attention_defines(dim, vdim)), f"tkb_attn_sink_simt_{_suffix(cache.dtype)}")(
+        _ptr(q), _ptr(out), _ptr(cache), _ptr(token_seq), _ptr(positions), _ptr(page_indptr), _ptr(page_ids), _ptr(rows),
+        c_int(n_rows), _ptr(sinks), c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale),
+        c_float(softcap or 0.0), c_int(window or 0), c_int(cache.shape[0]), _ptr(status), _stream()), "attn_sink")
+
+
 def prepare_modules(modules) -> None:
     """Build and load the listed (source file, constants) modules."""
     for source, defines in modules:

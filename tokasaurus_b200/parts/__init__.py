@@ -13,11 +13,13 @@ from tokasaurus_b200.parts.base import (  # noqa: F401
 )
 from tokasaurus_b200.parts.norm import LayerNorm, RMSNorm  # noqa: F401
 from tokasaurus_b200.parts.conv import ShortConv  # noqa: F401
-from tokasaurus_b200.parts.rope import NoPositionEncoding, RotaryEncoding  # noqa: F401
+from tokasaurus_b200.parts.rope import NoPositionEncoding, RotaryEncoding, SinusoidalPositions  # noqa: F401
 from tokasaurus_b200.parts.attention import PagedAttention  # noqa: F401
-from tokasaurus_b200.parts.mlp import GatedMLP, PolyNormMLP, RoutedExperts  # noqa: F401
-from tokasaurus_b200.parts.recurrent import GatedLinearRecurrence  # noqa: F401
+from tokasaurus_b200.parts.mlp import ClampedGLU, GatedMLP, PolyNormMLP, RoutedExperts  # noqa: F401
+from tokasaurus_b200.parts.recurrent import DecayedLinearAttention, GatedLinearRecurrence  # noqa: F401
+from tokasaurus_b200.parts.state_space import SelectiveStateSpace  # noqa: F401
+from tokasaurus_b200.parts.sink_attention import SinkAttention  # noqa: F401
 from tokasaurus_b200.parts.latent_attention import LatentAttention  # noqa: F401
-from tokasaurus_b200.parts.block import PreNormBlock  # noqa: F401
+from tokasaurus_b200.parts.block import OutputNormBlock, PreNormBlock  # noqa: F401
 from tokasaurus_b200.parts.embedding import OutputHead, TokenEmbedding  # noqa: F401
 from tokasaurus_b200.parts.model import DecoderModel, LayerCall  # noqa: F401

@@ -157,10 +157,12 @@ class InputStage(Part):
 class ResidualStream:
     """The running sum of a token's representation, held in float32, plus one pending
     update in the engine's dtype that the next norm adds before it normalises (so the add
-    costs no extra pass over memory)."""
+    costs no extra pass over memory).  ``h``: the same rows as ``x`` in the activation type, if the kernel that made
+    ``x`` wrote them too (blocks whose sublayers read the stream itself)."""
 
-    __slots__ = ("x", "delta")
+    __slots__ = ("x", "delta", "h")
 
-    def __init__(self, x: "torch.Tensor", delta: "torch.Tensor | None" = None):
+    def __init__(self, x: "torch.Tensor", delta: "torch.Tensor | None" = None, h: "torch.Tensor | None" = None):
         self.x = x
         self.delta = delta
+        self.h = h

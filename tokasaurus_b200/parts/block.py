@@ -88,3 +88,67 @@ class PreNormBlock(Part):
         x = torch.empty((rows.numel(), stream.x.shape[1]), dtype=stream.x.dtype, device=stream.x.device)
         ops.gather_rows(stream.x, rows, x)
         return ResidualStream(x)
+
+
+class OutputNormBlock(Part):
+    """A block whose sublayers read the residual stream itself and whose norms sit on the sublayers' OUTPUTS:
+
+        x <- x + mult * scale1 * norm1(mixer(x)),      x <- x + mult * scale2 * norm2(ffn(x))
+
+    ``mult`` is a number, ``scale1`` / ``scale2`` optional per-channel vectors (a layer scale; tensor names).  The
+    norms are RMS norms (``parts.norm.RMSNorm``: weight and eps).  The stream stays float32; the kernel that adds a
+    sublayer's normed output also writes the new stream in the activation type for the sublayer that reads it next.
+    A mixer may carry an ``out_bias`` (the bias of its output projection), which is added before the norm."""
+
+    def __init__(self, mixer: Mixer, mixer_norm, ffn: FeedForward | None, ffn_norm, mult: float = 1.0,
+                 mixer_scale_name: str | None = None, ffn_scale_name: str | None = None):
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a block has a feed-forward and its norm, or neither")
+        self.mixer, self.mixer_norm, self.ffn, self.ffn_norm = mixer, mixer_norm, ffn, ffn_norm
+        self.mult = float(mult)
+        self.scale_names = (mixer_scale_name, ffn_scale_name if ffn is not None else None)
+        self.scales: list[torch.Tensor | None] = [None, None]
+        self.width = mixer_norm.width
+        self.dtype: torch.dtype | None = None
+
+    def parts(self):
+        return tuple(p for p in (self.mixer, self.mixer_norm, self.ffn, self.ffn_norm) if p is not None)
+
+    def weight_specs(self):
+        from tokasaurus_b200.parts.base import WeightSpec
+        own = tuple(WeightSpec(n, (self.width,), role="vector") for n in self.scale_names if n is not None)
+        return tuple(s for p in self.parts() for s in p.weight_specs()) + own
+
+    def kernel_modules(self, dtype):
+        return (("post_norm.cu", None),) + tuple(m for p in self.parts() for m in p.kernel_modules(dtype))
+
+    def bind(self, weights, rt) -> None:
+        for p in self.parts():
+            p.bind(weights, rt)
+        self.scales = [weights[n].contiguous() if n is not None else None for n in self.scale_names]
+        self.dtype = rt.dtype
+
+    def state_needs(self) -> dict:
+        return {}
+
+    def _input(self, stream: ResidualStream) -> torch.Tensor:
+        if self.dtype == torch.float32:
+            return stream.x
+        if stream.h is None:
+            stream.h = torch.empty(stream.x.shape, dtype=self.dtype, device=stream.x.device)
+            ops.cast_rows(stream.x, stream.h)
+        return stream.h
+
+    def _add(self, stream: ResidualStream, y: torch.Tensor, norm, scale, bias=None) -> None:
+        h = None if self.dtype == torch.float32 else torch.empty(stream.x.shape, dtype=self.dtype, device=y.device)
+        ops.scaled_norm_add(stream.x, y, norm.weight, scale, self.mult, norm.eps, h, bias)
+        stream.h = h
+
+    def forward(self, ctx, stream: ResidualStream, cache, out_rows=None, stage_state=None) -> ResidualStream:
+        y = self.mixer.forward(ctx, self._input(stream), cache, out_rows)
+        if out_rows is not None:
+            stream = PreNormBlock._cut(stream, out_rows)
+        self._add(stream, y, self.mixer_norm, self.scales[0], getattr(self.mixer, "out_bias", None))
+        if self.ffn is not None:
+            self._add(stream, self.ffn.forward(ctx, self._input(stream)), self.ffn_norm, self.scales[1])
+        return stream

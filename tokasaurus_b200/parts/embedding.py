@@ -10,8 +10,11 @@ from tokasaurus_b200.parts.base import Norm, Part, ResidualStream, WeightSpec
 
 
 class TokenEmbedding(Part):
-    def __init__(self, vocab: int, width: int, weight_name: str, scale: float = 1.0):
-        """``scale`` multiplies the gathered rows (in float32, on their way into the residual stream)."""
+    def __init__(self, vocab: int, width: int, weight_name: str, scale: float = 1.0, positions=None):
+        """``scale`` multiplies the gathered rows (in float32, on their way into the residual stream).  ``positions``:
+        a ``parts.rope.SinusoidalPositions`` whose vectors are added to the rows, or None."""
+        self.positions = positions
+        self.pos_freq: torch.Tensor | None = None
         self.vocab = vocab
         self.width = width
         self.weight_name = weight_name
@@ -21,13 +24,20 @@ class TokenEmbedding(Part):
     def weight_specs(self):
         return (WeightSpec(self.weight_name, (self.vocab, self.width)),)
 
+    def kernel_modules(self, dtype):
+        return (("post_norm.cu", None),) if self.positions is not None else ()
+
     def bind(self, weights, rt) -> None:
         self.table = weights[self.weight_name]
+        if self.positions is not None:
+            self.pos_freq = self.positions.inv_freq().to(rt.device)
 
     def forward(self, ctx) -> ResidualStream:
         x = torch.empty((ctx.n_tokens, self.width), dtype=torch.float32, device=self.table.device)
         ops.embed_gather(self.table, ctx.token_ids, ctx.token_seq, ctx.seq_slot, ctx.last_token, x, ctx.status,
                          self.scale)
+        if self.pos_freq is not None:
+            ops.add_sinusoid(x, ctx.positions, self.pos_freq)
         return ResidualStream(x)
 
 

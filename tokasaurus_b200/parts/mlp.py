@@ -59,6 +59,36 @@ class GatedMLP(FeedForward):
         return ops.linear(act, self.w_down)
 
 
+class ClampedGLU(FeedForward):
+    """``down(g * sigmoid(alpha * g) * (u + 1))`` with ``g = min(gate(h), limit)`` and ``u = clamp(up(h), -limit,
+    limit)``; no biases.  The gate and up matrices are stacked into one product; the update leaves as float32 (a norm
+    reads it)."""
+
+    def __init__(self, width: int, inner: int, limit: float, gate_name: str, up_name: str, down_name: str,
+                 alpha: float = 1.702):
+        self.width, self.inner, self.limit, self.alpha = width, inner, float(limit), float(alpha)
+        self.names = (gate_name, up_name, down_name)
+
+    def weight_specs(self):
+        g, u, d = self.names
+        return (WeightSpec(g, (self.inner, self.width)), WeightSpec(u, (self.inner, self.width)),
+                WeightSpec(d, (self.width, self.inner)))
+
+    def kernel_modules(self, dtype):
+        return (("post_norm.cu", None),)
+
+    def bind(self, weights, rt) -> None:
+        g, u, d = self.names
+        self.w_gate_up = torch.cat([weights[g], weights[u]], dim=0).contiguous()
+        self.w_down = weights[d].contiguous()
+
+    def forward(self, ctx, h):
+        gu = ops.linear(h, self.w_gate_up)
+        act = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
+        ops.clamped_glu(gu, act, self.limit, self.alpha)
+        return ops.linear(act, self.w_down, out_dtype=torch.float32)
+
+
 class PolyNormMLP(FeedForward):
     """``down(act(up(h)))`` with the PolyNorm activation ``act(z) = a N(z) + b N(z^2) + c N(z^3) + e``, where powers
     are taken element by element and N divides a token's vector of inner values by its root mean square

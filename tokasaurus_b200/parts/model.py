@@ -111,8 +111,11 @@ class DecoderModel(Part):
         return needs
 
     def forward(self, ctx) -> torch.Tensor:
-        """Run this step's tokens; return float32 logits [len(ctx.logit_rows), vocab]."""
+        """Run this step's tokens; return float32 logits [len(ctx.logit_rows), vocab].  If the context carries a list
+        ``layer_outputs``, a copy of the residual stream after every layer call is appended to it (pending updates
+        folded in), for looking at a model layer by layer."""
         stream = self.embedding.forward(ctx)
+        taps = getattr(ctx, "layer_outputs", None)
         last = len(self.run_order) - 1
         rows = None if ctx.all_rows_wanted else ctx.logit_rows
         for i, call in enumerate(self.run_order):
@@ -122,4 +125,9 @@ class DecoderModel(Part):
                 stream = self.blocks[call.block].forward(ctx, stream, cache, rows if i == last else None, states)
             else:
                 stream = self.blocks[call.block].forward(ctx, stream, cache, rows if i == last else None)
+            if taps is not None:
+                x = stream.x.clone()
+                if stream.delta is not None:
+                    x += stream.delta.sum(0) if stream.delta.dim() == 3 else stream.delta
+                taps.append(x)
         return self.head.forward(ctx, stream)

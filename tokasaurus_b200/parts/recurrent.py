@@ -62,3 +62,66 @@ class GatedLinearRecurrence(Mixer):
             ops.gather_rows(o, out_rows, cut)
             o = cut
         return ops.linear(o, self.w_o)
+
+
+class DecayedLinearAttention(Mixer):
+    """Linear attention with one fixed decay a head:
+
+        S_t = lambda_h S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t,   q, k, v = silu(W_q h), silu(W_k h), silu(W_v h),
+
+    then an RMS norm over all heads' o_t together (one weight vector), a gate sigmoid(W_g h), and the output projection.
+    The state (float32, S^T per head, zero at admission) lives in the request's slot; the four projections are one
+    matrix product with a float32 result, the recurrence, the norm and the gate are float32.  The walk over the
+    tokens is the kernel that the selective state space uses too (csrc/decay_recurrence.cu)."""
+
+    graph_safe = True
+
+    def __init__(self, width: int, n_heads: int, dim: int, vdim: int, decay, norm_eps: float, q_name: str, k_name: str,
+                 v_name: str, g_name: str, norm_name: str, o_name: str):
+        if len(decay) != n_heads:
+            raise ValueError(f"{len(decay)} decays for {n_heads} heads")
+        self.width, self.n_heads, self.dim, self.vdim = width, n_heads, dim, vdim
+        self.decay = tuple(float(d) for d in decay)
+        self.norm_eps = float(norm_eps)
+        self.names = dict(q=q_name, k=k_name, v=v_name, g=g_name, norm=norm_name, o=o_name)
+        self.defines = ops.decay_recurrence_defines(dim, vdim)  # refuses sizes the kernel does not take
+
+    def weight_specs(self):
+        n, H, d, e = self.names, self.n_heads, self.dim, self.vdim
+        return (WeightSpec(n["q"], (H * d, self.width)), WeightSpec(n["k"], (H * d, self.width)),
+                WeightSpec(n["v"], (H * e, self.width)), WeightSpec(n["g"], (H * e, self.width)),
+                WeightSpec(n["o"], (self.width, H * e)), WeightSpec(n["norm"], (H * e,), role="vector"))
+
+    def kernel_modules(self, dtype):
+        return (("decay_recurrence.cu", self.defines), ("post_norm.cu", None))
+
+    def cache_need(self):
+        return StateNeed((self.n_heads * self.vdim * self.dim,), "float32")  # S^T: [head][value][key channel]
+
+    def bind(self, weights, rt) -> None:
+        n = self.names
+        self.w_qkvg = torch.cat([weights[n["q"]], weights[n["k"]], weights[n["v"]], weights[n["g"]]], dim=0).contiguous()
+        self.w_o = weights[n["o"]].contiguous()
+        self.norm_w = weights[n["norm"]].contiguous()
+        self.decay_t = torch.tensor(self.decay, dtype=torch.float64).to(torch.float32).to(rt.device)
+
+    def forward(self, ctx, h, cache, out_rows=None):
+        H, d, e = self.n_heads, self.dim, self.vdim
+        T = h.shape[0]
+        proj = ops.linear(h, self.w_qkvg, out_dtype=torch.float32)
+        q, k = proj[:, :H * d], proj[:, H * d:2 * H * d]
+        v, g = proj[:, 2 * H * d:2 * H * d + H * e], proj[:, 2 * H * d + H * e:]
+        raw = torch.empty((T, H * e), dtype=torch.float32, device=h.device)
+        ops.decay_walk(q, k, v, 1, None, self.decay_t, None, cache.state, raw, ctx.seq_slot, ctx.seq_q_start,
+                       ctx.seq_q_len, ctx.n_seqs, H, d, e, True, self.defines, cache.writable)
+        if out_rows is not None:
+            raw, g = _rows(raw, out_rows), _rows(g.contiguous(), out_rows)
+        o = torch.empty(raw.shape, dtype=h.dtype, device=h.device)
+        ops.gated_group_norm(raw, g, self.norm_w, o, 1, self.norm_eps, gate_first=False)
+        return ops.linear(o, self.w_o, out_dtype=torch.float32)
+
+
+def _rows(t: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    cut = torch.empty((rows.numel(), t.shape[1]), dtype=t.dtype, device=t.device)
+    ops.gather_rows(t, rows, cut)
+    return cut

@@ -65,3 +65,21 @@ class RotaryEncoding(PositionEncoding):
         mid = (1 - smooth) * scaled / self.factor + smooth * scaled
         is_mid = ~(wavelen < high_wavelen) & ~(wavelen > low_wavelen)
         return torch.where(is_mid, mid, scaled).to(torch.float32)
+
+
+class SinusoidalPositions(PositionEncoding):
+    """A position vector added to the embedding: entry 2i is sin(p * base^(-2i / width)), entry 2i + 1 the cosine of
+    the same angle.  The frequencies are worked out in float64 and kept as float32; the angle is their float32
+    product with the position, formed in the kernel."""
+
+    kind = "additive"
+    rotary_dim = 0
+
+    def __init__(self, width: int, base: float = 10000.0):
+        self.width = int(width)
+        self.base = float(base)
+
+    def inv_freq(self) -> torch.Tensor:
+        """float32 [ceil(width / 2)], on the CPU."""
+        i = torch.arange((self.width + 1) // 2, dtype=torch.float64)
+        return (self.base ** (-2.0 * i / self.width)).to(torch.float32)

@@ -1,0 +1,86 @@
+"""Grouped-query attention over a sliding window with a cap on the scores and a sink in the softmax.
+
+q = W_q h + b_q, k = W_k h + b_k (``dim`` values a head), v = W_v h + b_v (``vdim`` values a head; the two sizes may
+differ); optionally every q head and every k head is divided by its root mean square (an RMS norm without a weight);
+no rotation.  With c the cap,
+
+    s_ij = c * tanh(scale * q_i . k_j / c),      o_i = sum_j exp(s_ij) v_j / (exp(sink_h) + sum_j exp(s_ij))
+
+over the last ``window`` positions (the query's own included; None: all).  The sink is a learned number per head that
+takes part in the denominator only.  The output projection may carry a bias (``out_bias``), which the block adds.
+
+A token's key and value of one key/value head are cached side by side as one row [k | v] (one plane): rows
+``[page, kv head, slot, dim + vdim]``.  The projections are one product with a float32 result; biases, the unit norms,
+scores, weights and sums are float32.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from tokasaurus_b200.kernels import ops
+from tokasaurus_b200.parts.base import Mixer, PagedCacheNeed, WeightSpec
+
+
+class SinkAttention(Mixer):
+    graph_safe = True
+
+    def __init__(self, width: int, n_heads: int, n_kv_heads: int, dim: int, vdim: int, scale: float,
+                 softcap: float | None, window: int | None, norm_eps: float, q_name: str, k_name: str, v_name: str,
+                 o_name: str, sink_name: str | None, bias_names: tuple[str, str, str] | None = None,
+                 out_bias_name: str | None = None, unit_norm: bool = True):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"n_heads={n_heads} is not a multiple of n_kv_heads={n_kv_heads}")
+        self.width, self.n_heads, self.n_kv_heads, self.dim, self.vdim = width, n_heads, n_kv_heads, dim, vdim
+        self.scale = float(scale)
+        self.softcap = float(softcap) if softcap else None
+        self.window = int(window) if window else None
+        self.norm_eps, self.unit_norm = float(norm_eps), bool(unit_norm)
+        self.names = (q_name, k_name, v_name, o_name)
+        self.sink_name, self.bias_names, self.out_bias_name = sink_name, bias_names, out_bias_name
+        self.defines = ops.sink_attention_defines(dim, vdim)
+        self.sinks = self.qkv_bias = self.out_bias = None
+
+    def weight_specs(self):
+        q, k, v, o = self.names
+        H, G, d, e = self.n_heads, self.n_kv_heads, self.dim, self.vdim
+        specs = [WeightSpec(q, (H * d, self.width)), WeightSpec(k, (G * d, self.width)),
+                 WeightSpec(v, (G * e, self.width)), WeightSpec(o, (self.width, H * e))]
+        if self.bias_names is not None:
+            specs += [WeightSpec(n, (rows,), role="vector") for n, rows in zip(self.bias_names, (H * d, G * d, G * e))]
+        if self.out_bias_name is not None:
+            specs.append(WeightSpec(self.out_bias_name, (self.width,), role="vector"))
+        if self.sink_name is not None:
+            specs.append(WeightSpec(self.sink_name, (H,), role="vector"))
+        return tuple(specs)
+
+    def kernel_modules(self, dtype):
+        return (("attention_sink.cu", self.defines),)
+
+    def cache_need(self):
+        return PagedCacheNeed(self.n_kv_heads, self.dim + self.vdim, self.window, planes=1)
+
+    def bind(self, weights, rt) -> None:
+        q, k, v, o = self.names
+        self.w_qkv = torch.cat([weights[q], weights[k], weights[v]], dim=0).contiguous()
+        self.w_o = weights[o].contiguous()
+        if self.bias_names is not None:
+            self.qkv_bias = torch.cat([weights[n].float() for n in self.bias_names]).contiguous()
+        if self.out_bias_name is not None:
+            self.out_bias = weights[self.out_bias_name].contiguous()
+        if self.sink_name is not None:
+            self.sinks = weights[self.sink_name].contiguous()
+
+    def forward(self, ctx, h, cache, out_rows=None):
+        H, G, d, e = self.n_heads, self.n_kv_heads, self.dim, self.vdim
+        T = h.shape[0]
+        tables = ctx.tables[cache.group]
+        qkv = ops.linear(h, self.w_qkv, out_dtype=torch.float32)
+        q = torch.empty((T, H * d), dtype=h.dtype, device=h.device)
+        ops.sink_attn_prep(qkv, self.qkv_bias, self.unit_norm, self.norm_eps, q, cache.k, ctx.positions, ctx.token_seq,
+                           tables.indptr, tables.page_ids, H, G, d, e, cache.page_size, cache.writable, ctx.status)
+        n_rows = T if out_rows is None else out_rows.numel()
+        attn = torch.empty((n_rows, H * e), dtype=h.dtype, device=h.device)
+        ops.attn_sink(q, attn, cache.k, ctx.token_seq, ctx.positions, tables.indptr, tables.page_ids, out_rows, n_rows,
+                      self.sinks, H, G, d, e, cache.page_size, self.scale, self.softcap, self.window, ctx.status)
+        return ops.linear(attn, self.w_o, out_dtype=torch.float32)
