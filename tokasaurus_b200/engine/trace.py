@@ -74,11 +74,13 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time (each rounded up to a multiple of 64)")
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--slots", type=int, default=4,
+                    help="requests that may be live at a time: the engine's state slots (they are used again)")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
-    replayer = TraceReplayer(args.model, args.dtype, args.max_tokens, args.page_size, args.device)
+    replayer = TraceReplayer(args.model, args.dtype, args.max_tokens, args.page_size, args.device, args.slots)
     for line in sys.stdin:
         line = line.strip()
         if not line:
