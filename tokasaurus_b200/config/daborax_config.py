@@ -161,8 +161,8 @@ class DaboraxConfig:
             if j is not None:
                 if not isinstance(j, int) or isinstance(j, bool) or not 0 <= j < i or layers[j].weights_of is not None:
                     raise ConfigError(f"{where}.weights_of={j!r} must name an earlier layer that has tensors of its own")
-                if (layers[j].type, layers[j].mixer, layers[j].mlp) != (layer.type, layer.mixer, layer.mlp):
-                    raise ConfigError(f"{where} runs with layer {j}'s tensors but differs from it")
+                if layers[j].type != layer.type or (layers[j].mlp is None) != (layer.mlp is None):
+                    raise ConfigError(f"{where}.weights_of={j}: layer {j} has another mixer type or feed-forward")
             layers.append(layer)
         eps = float((d.get("norm") or {}).get("eps", 1e-6))
         if not (eps > 0 and math.isfinite(eps)):

@@ -37,10 +37,12 @@ def build_daborax(cfg: DaboraxConfig) -> DecoderModel:
     blocks, order = [], []
     block_of: dict[int, int] = {}
     for i, layer in enumerate(cfg.layers):
-        if layer.weights_of is not None:
-            order.append(LayerCall(block_of[layer.weights_of]))
+        j = layer.weights_of
+        if j is not None and (cfg.layers[j].mixer, cfg.layers[j].mlp) == (layer.mixer, layer.mlp):
+            order.append(LayerCall(block_of[j]))  # the same block once more, with a cache entry of this call's own
             continue
-        p, m = f"l{i}", layer.mixer
+        # (an entry that names layer j's tensors but other constants: a block of its own over the same tensors)
+        p, m = f"l{i if j is None else j}", layer.mixer
         if isinstance(m, StateSpaceConfig):
             mixer = SelectiveStateSpace(W, m.heads, m.vdim, m.state, m.groups, m.norm_groups, m.taps, eps,
                                         in_name=f"{p}.mix.in", conv_name=f"{p}.mix.conv", conv_bias_name=f"{p}.mix.conv.b",
