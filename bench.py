@@ -2,7 +2,7 @@
 random weights (the metric and configuration of BASELINE.json's configs[2]).
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 2|3|4]
-    python bench.py --design sozurax        (another workload, see run_design; the default workload and its output line are unchanged)
+    python bench.py --design sozurax|daborax   (another workload, see run_design; the default workload and its output line are unchanged)
 
 Prints ONE JSON line.  ``value``: decoded tokens a second at batch 8, each request holding a
 2,048-token prompt in the cache, timed on the device with CUDA events around K decode steps
@@ -160,7 +160,8 @@ def prefill_flops(m: dict, T: int, rows: int = 1) -> float:
     return linear + attention
 
 
-TIMED_OPS = ("add_layernorm", "add_layernorm_conv1", "short_conv", "polynorm", "gated_recurrence", "latent_prep",
+TIMED_OPS = ("scaled_norm_add", "cast_rows", "add_sinusoid", "clamped_glu", "gated_group_norm", "ssm_prep", "decay_walk",
+             "sink_attn_prep", "attn_sink", "attn_sink_tiles", "add_layernorm", "add_layernorm_conv1", "short_conv", "polynorm", "gated_recurrence", "latent_prep",
              "rotate_pairs", "latent_attn", "moe_route", "moe_order", "moe_gather", "moe_gemm", "moe_combine",
              "gemm_tcgen05_grouped", "embed_gather", "add_rmsnorm", "rope_kv_write", "rope_kv_write_partials", "linear_decode", "linear_smallm",
              "linear_smallm_gated", "silu_mul", "gather_rows", "attn_decode_mma", "attn_decode_rope_mma", "attn_prefill_mma",
@@ -652,6 +653,32 @@ def run_reference(args) -> dict:
     return out
 
 
+def daborax_configs(name: str) -> dict:
+    """Layer sizes for ``--design daborax``: two sizes that resemble a real model's layers, each as a Daborax decoder
+    (decayed linear attention, windowed attention with capped scores and a sink, a selective state space, and the first
+    layer's tensors once more; every layer with a clamped gated feed-forward) and as the closest existing model, a Llama
+    decoder of the same width, depth, vocabulary and feed-forward size."""
+    sizes = dict(w2048=dict(width=2048, heads=16, ff=8192, att_heads=32, att_kv=8, ssm_heads=64, ssm_groups=8),
+                 w4096=dict(width=4096, heads=32, ff=14336, att_heads=32, att_kv=8, ssm_heads=128, ssm_groups=8))
+    z = sizes[name]
+    W = z["width"]
+    mlp = dict(kind="dense", ff=z["ff"], limit=7.0)
+    lin = dict(type="lightning", mixer=dict(heads=z["heads"], dim=128, vdim=128,
+                                            decay=[1.0 - 2.0 ** -(2 + 6 * h / (z["heads"] - 1)) for h in range(z["heads"])]), mlp=mlp)
+    att = dict(type="attention", mixer=dict(heads=z["att_heads"], kv_heads=z["att_kv"], dim=W // z["att_heads"],
+                                            vdim=W // z["att_heads"], mask=dict(size=1024), scale=(W // z["att_heads"]) ** -0.5,
+                                            softcap=50.0), mlp=mlp)
+    ssm = dict(type="mamba2", mixer=dict(heads=z["ssm_heads"], vdim=64, state=128, groups=z["ssm_groups"],
+                                         norm_groups=z["ssm_groups"], conv=4), mlp=mlp)
+    dab = dict(architecture="Daborax", vocab=32000, width=W, norm=dict(eps=1e-6), embedding=dict(scale=1.0), residual_mult=0.5,
+               layers=[lin, att, ssm, dict(lin, weights_of=0)])
+    llama = dict(architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=4, hidden_size=W,
+                 num_attention_heads=z["att_heads"], num_key_value_heads=z["att_kv"], intermediate_size=z["ff"],
+                 vocab_size=32000, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                 max_position_embeddings=131072)
+    return dict(daborax=dab, llama=llama)
+
+
 def design_configs(name: str) -> dict:
     """Layer sizes for ``--design sozurax``: two sizes that resemble a real model's layers, each as a Sozurax decoder
     (a recurrent layer with a dense feed-forward, a latent-attention layer with routed experts, a second recurrent
@@ -681,8 +708,8 @@ def design_configs(name: str) -> dict:
 
 
 def run_design(args) -> dict:
-    """``--design sozurax``: prefill (one 2,048-token prompt in one step) and decode (batch 8 and 64, prompts of 2,048
-    tokens in the cache) of the Sozurax decoder at two layer sizes beside a Llama decoder of equal size, random weights,
+    """``--design sozurax|daborax``: prefill (one 2,048-token prompt in one step) and decode (batch 8 and 64, prompts of
+    2,048 tokens in the cache) of that decoder at two layer sizes beside a Llama decoder of equal size, random weights,
     bfloat16, with the CUDA-event time of each kind of kernel in one prefill step and one decode step of both."""
     import numpy as np
     import torch
@@ -694,10 +721,13 @@ def run_design(args) -> dict:
 
     peaks, peak_src = load_peaks()
     prompt_len, page_size = 2048, 16
-    out = dict(design="sozurax", dtype="bf16", data="synthetic", peaks=dict(peaks, source=peak_src), sizes={})
+    out = dict(design=args.design, dtype="bf16", data="synthetic", peaks=dict(peaks, source=peak_src), sizes={})
+    configs_of = daborax_configs if args.design == "daborax" else design_configs
     for size in ("w2048", "w4096"):
         res = {}
-        for arch, cfg in design_configs(size).items():
+        for arch, cfg in configs_of(size).items():
+            if args.design_arch and arch != args.design_arch:
+                continue
             eng = Engine(config_dict=cfg, random_weights=0, dtype="bfloat16", page_size=page_size,
                          kv_cache_num_tokens=64 * 2304, max_tokens_per_forward=8192, max_seqs_per_forward=64, device="cuda:0")
             runner, cache, sampler = eng.runner, eng.runner.cache, eng.sampler
@@ -802,7 +832,8 @@ def main() -> int:
     ap.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference arm may take")
     ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4],
                     help="2: the headline metric (default); 3 and 4: the further workloads, see run_further")
-    ap.add_argument("--design", default=None, choices=["sozurax"],
+    ap.add_argument("--design-arch", default=None, help="with --design: only this arm (the design's name or 'llama')")
+    ap.add_argument("--design", default=None, choices=["sozurax", "daborax"],
                     help="instead of the headline workload: this design's prefill and decode at two layer sizes beside "
                          "the Llama decoder of equal size (see run_design)")
     args = ap.parse_args()

@@ -274,6 +274,18 @@ def test_sink_attention_window_edges(ops, dtype, dim, vdim, page, heads, kv):
                 ops.attn_sink(qd, out, cache, i32([0] * m), i32(pos), i32([0, need]), i32(table[:need]), None, m,
                               sinks.to(DEV), heads, kv, dim, vdim, page, scale, cap, window, status)
                 got.append(out.float().cpu())
+                if ops.can_use_attn_sink_tc(DT[dtype], dim, vdim):
+                    # the same on the tensor cores: as a portion and, if it is one token, as a single token; beside a
+                    # second request of one token (the first request's first token once more, from its own page)
+                    out2 = torch.full((m + 1, heads * vdim), float("nan"), dtype=DT[dtype], device=DEV)
+                    q2 = torch.cat([qd, qd[:1] if at == 0 else q_first])
+                    if at == 0:
+                        q_first = qd[:1].clone()
+                    ops.attn_sink_tc(q2, out2, cache, i32([0, m]), i32([m, 1]), i32([at + m, 1]), i32([0, need, need + 1]),
+                                     i32(table[:need] + table[:1]), 2, sinks.to(DEV), heads, kv, dim, vdim, page, scale, cap,
+                                     window, status, portions=m > 1)
+                    assert rel_err(out2[:m].float().cpu(), want[at:at + m]) < 3e-2, ("tensor cores", far_at, cut[:2], at)
+                    assert rel_err(out2[m:].float().cpu(), want[:1]) < 3e-2
                 at += m
             got = torch.cat(got)
             assert int(status.item()) == 0

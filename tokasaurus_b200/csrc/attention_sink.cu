@@ -14,6 +14,16 @@
 // portions and single tokens; lane j scores key base + j, probabilities are passed round by shuffle while lane d
 // sums output elements d, d + 32, ...  Scores, weights and sums are float32.
 //
+//
+// In bfloat16, for key sizes that are multiples of 16 and value sizes that are multiples of 16, two tensor-core kernels
+// (mma.sync m16n8k16, float32 scores, weights rounded to bfloat16 for their product with the values) take the place of
+// the FP32-pipe kernel.  Both stage 64 cached rows at a time in shared memory (cp.async, two buffers; a row's key and
+// value arrive in one copy) and keep a running softmax that the sink opens.  attn_sink_tiles: a block owns 64 queries
+// of one request's portion and one query head, a warp 16 of them.  attn_sink_single: a block owns a request that
+// brings one token and one key/value head; the MMA rows are that head's query heads, the four warps take every
+// fourth group of 16 keys and are merged through shared memory.  Blocks find their work from the step's request
+// table themselves, so a launch depends on the step's shape only.
+//
 // Compile with -DTKB_QK=<query/key size> -DTKB_VD=<value size>.
 #include "common.cuh"
 #include <float.h>
@@ -237,3 +247,380 @@ int attn_launch(const void* q, void* out, const void* cache, const int* token_se
 
 TKB_SINK_EXPORTS(f32, float)
 TKB_SINK_EXPORTS(bf16, __nv_bfloat16)
+
+// ------------------------------------------------------------------------------------------------ tensor cores
+#if (TKB_QK % 16 == 0) && (TKB_VD % 16 == 0)
+#define TKB_SINK_TC 1
+namespace {
+
+using bf16 = __nv_bfloat16;
+constexpr int KT = 64;            // keys per staged tile
+constexpr int RS = ROW + 8;       // row stride in shared memory (elements): 16 bytes of padding keep the banks apart
+constexpr int KSTEPS = QK / 16;   // k-steps of q . k
+constexpr int VT = VD / 8;        // 8-column tiles of the output
+constexpr float NEG_BIG = -1e30f;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// cap * tanh(s / cap) in units of log2: tanh(x) = 1 - 2 / (e^(2x) + 1), the exponential of a bounded argument
+__device__ __forceinline__ float capped_log2(float s, float softcap, float inv_cap) {
+  if (softcap > 0.f) {
+    const float x = fminf(fmaxf(s * inv_cap, -15.f), 15.f);
+    const float e = ex2(2.f * LOG2E * x);
+    // near zero 1 - 2 / (e + 1) loses digits: there tanh(x) = x - x^3 / 3 + 2 x^5 / 15 is exact to float32
+    const float x2 = x * x;
+    const float t = fabsf(x) < 0.125f ? x * (1.f - x2 * (0.33333334f - x2 * (0.13333334f - x2 * 0.053968254f)))
+                                       : 1.f - __fdividef(2.f, e + 1.f);
+    s = softcap * t;
+  }
+  return s * LOG2E;
+}
+
+// Keys k0 .. k0 + 63 of the request into one buffer: a cached row [k | v] is one run of 16-byte pieces.  Rows outside
+// [k_lo, k_hi], on a page that is gone or beyond the pool, are zeros.
+__device__ __forceinline__ void stage_tile(bf16* buf, const bf16* __restrict__ cache, const int* __restrict__ table,
+                                           int k0, int k_lo, int k_hi, int kvh, int nkv, int ps, int num_pages,
+                                           bool& bad, int tid) {
+  constexpr int CH = ROW / 8;
+  for (int idx = tid; idx < KT * CH; idx += 128) {
+    const int r = idx / CH, c = idx - r * CH;
+    const int key = k0 + r;
+    bf16* dst = buf + r * RS + c * 8;
+    int page = -1;
+    if (key >= k_lo && key <= k_hi) page = checked_page(table[key / ps], num_pages, bad);
+    if (page >= 0) cp_async16(smem_u32(dst), cache + (((size_t)page * nkv + kvh) * ps + (key % ps)) * ROW + c * 8);
+    else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+// One warp, 16 rows, NT groups of 8 keys that start at row `kr0` of the staged tile (key index key0): scores, running
+// softmax, and the weighted sum of values.  lim_lo / lim_hi: the keys each of the thread's two rows may see.
+template <int NT>
+__device__ __forceinline__ void attend(const bf16* buf, int kr0, int key0, const uint32_t (&qf)[KSTEPS][4], float (&o)[VT][4],
+                                       float (&m)[2], float (&l)[2], const int (&lim_lo)[2], const int (&lim_hi)[2],
+                                       float scale, float softcap, float inv_cap, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  float sc[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; nt++) {
+    sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+    const bf16* krow = buf + (kr0 + nt * 8 + g) * RS + 2 * t;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ks++) {
+      const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks * 16);
+      const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ks * 16 + 8);
+      mma_bf16(sc[nt], qf[ks], b0, b1);
+    }
+  }
+  float alpha[2];
+#pragma unroll
+  for (int h = 0; h < 2; h++) {
+    float mx = NEG_BIG;
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        const int key = key0 + nt * 8 + 2 * t + e;
+        float v = capped_log2(sc[nt][h * 2 + e] * scale, softcap, inv_cap);
+        if (key < lim_lo[h] || key > lim_hi[h]) v = -INFINITY;
+        sc[nt][h * 2 + e] = v;
+        mx = fmaxf(mx, v);
+      }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m[h], mx);
+    alpha[h] = ex2(m[h] - m_new);
+    m[h] = m_new;
+    float sum = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        const float p = ex2(sc[nt][h * 2 + e] - m_new);
+        sc[nt][h * 2 + e] = p;
+        sum += p;
+      }
+    l[h] = l[h] * alpha[h] + sum;  // this thread's share; the four threads of a row are added up at the end
+  }
+#pragma unroll
+  for (int vt = 0; vt < VT; vt++) {
+    o[vt][0] *= alpha[0];
+    o[vt][1] *= alpha[0];
+    o[vt][2] *= alpha[1];
+    o[vt][3] *= alpha[1];
+  }
+#pragma unroll
+  for (int kk = 0; kk < NT / 2; kk++) {  // 16 keys at a time
+    uint32_t pf[4] = {pack_bf16(sc[2 * kk][0], sc[2 * kk][1]), pack_bf16(sc[2 * kk][2], sc[2 * kk][3]),
+                      pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]), pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3])};
+    const bf16* vbase = buf + (kr0 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * RS + QK + (lane >> 4) * 8;
+#pragma unroll
+    for (int vt = 0; vt < VT; vt += 2) {
+      uint32_t b[4];
+      ldmatrix_x4_trans(b, smem_u32(vbase + vt * 8));
+      mma_bf16(o[vt], pf, b[0], b[1]);
+      mma_bf16(o[vt + 1], pf, b[2], b[3]);
+    }
+  }
+}
+
+constexpr size_t TC_SMEM = (size_t)2 * KT * RS * sizeof(bf16);
+
+// Portions: block b takes the b-th 64-query tile of the step's requests that bring more than one token; blockIdx.y is
+// the query head.
+__global__ void __launch_bounds__(128)
+attn_sink_tiles_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ cache,
+                       const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
+                       const int* __restrict__ seq_kv_len, const int* __restrict__ page_indptr,
+                       const int* __restrict__ page_ids, int n_seqs, const float* __restrict__ sinks, int nh, int nkv,
+                       int ps, float scale, float softcap, int window, int num_pages, int* __restrict__ status) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* bufs = reinterpret_cast<bf16*>(smem_raw);
+  trigger_dependents();
+  int s = 0, tile = blockIdx.x;
+  for (; s < n_seqs; s++) {
+    const int n = seq_q_len[s];
+    const int tiles = n > 1 ? (n + KT - 1) / KT : 0;
+    if (tile < tiles) break;
+    tile -= tiles;
+  }
+  if (s >= n_seqs) return;
+  grid_dependency_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int h = blockIdx.y, kvh = h / (nh / nkv);
+  const int n_q = seq_q_len[s], start = seq_q_start[s];
+  const int pos0 = seq_kv_len[s] - n_q;  // position of the portion's first token
+  const int r0 = tile * KT;              // first query of the tile within the portion
+  const int rows = min(KT, n_q - r0);
+  const int* table = page_ids + page_indptr[s];
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+
+  uint32_t qf[KSTEPS][4];
+  int lim_lo[2], lim_hi[2];
+#pragma unroll
+  for (int hh = 0; hh < 2; hh++) {
+    const int r = warp * 16 + g + hh * 8;
+    const bool live = r < rows;
+    const int p = pos0 + r0 + r;
+    lim_hi[hh] = live ? p : -1;
+    lim_lo[hh] = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const bf16* qrow = q + ((size_t)(start + r0 + (live ? r : 0)) * nh + h) * QK;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ks++) {
+      qf[ks][hh] = live ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t) : 0u;
+      qf[ks][hh + 2] = live ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t) : 0u;
+    }
+  }
+  const float sink2 = sinks ? sinks[h] * LOG2E : NEG_BIG;
+  float m[2] = {sink2, sink2};
+  float l[2] = {(sinks && t == 0) ? 1.f : 0.f, (sinks && t == 0) ? 1.f : 0.f};
+  float o[VT][4];
+#pragma unroll
+  for (int vt = 0; vt < VT; vt++) o[vt][0] = o[vt][1] = o[vt][2] = o[vt][3] = 0.f;
+
+  const int p_first = pos0 + r0, p_last = pos0 + r0 + rows - 1;
+  const int k_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+  const int n_tiles = (p_last - k_lo) / KT + 1;
+  // the keys this warp's rows can see: [w_lo, w_hi]
+  const int w_first = pos0 + r0 + warp * 16;
+  const int w_lo = (window > 0 && w_first - window + 1 > 0) ? w_first - window + 1 : 0;
+  const int w_hi = min(p_last, w_first + 15);
+  bool bad = false;
+  stage_tile(bufs, cache, table, k_lo, k_lo, p_last, kvh, nkv, ps, num_pages, bad, tid);
+  cp_async_commit();
+  for (int it = 0; it < n_tiles; it++) {
+    bf16* cur = bufs + (it & 1) * KT * RS;
+    if (it + 1 < n_tiles) {
+      stage_tile(bufs + ((it + 1) & 1) * KT * RS, cache, table, k_lo + (it + 1) * KT, k_lo, p_last, kvh, nkv, ps, num_pages,
+                 bad, tid);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int key0 = k_lo + it * KT;
+    if (warp * 16 < rows && key0 <= w_hi && key0 + KT - 1 >= w_lo)  // warp-uniform: some row of the warp sees some key
+      attend<8>(cur, 0, key0, qf, o, m, l, lim_lo, lim_hi, scale, softcap, inv_cap, lane);
+    __syncthreads();  // the buffer is free for the tile after next
+  }
+  report_bad_page(bad, status);
+#pragma unroll
+  for (int hh = 0; hh < 2; hh++) {
+    l[hh] += __shfl_xor_sync(0xffffffffu, l[hh], 1);
+    l[hh] += __shfl_xor_sync(0xffffffffu, l[hh], 2);
+    const int r = warp * 16 + g + hh * 8;
+    if (r < rows) {
+      const float inv = l[hh] > 0.f ? 1.f / l[hh] : 0.f;
+      bf16* orow = out + ((size_t)(start + r0 + r) * nh + h) * VD + 2 * t;
+#pragma unroll
+      for (int vt = 0; vt < VT; vt++)
+        *reinterpret_cast<uint32_t*>(orow + vt * 8) = pack_bf16(o[vt][hh * 2] * inv, o[vt][hh * 2 + 1] * inv);
+    }
+  }
+}
+
+// Single tokens: blockIdx.x = request row (it leaves unless the request brings one token), blockIdx.y = key/value
+// head * head tiles + head tile (16 query heads a tile).
+__global__ void __launch_bounds__(128)
+attn_sink_single_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ cache,
+                        const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
+                        const int* __restrict__ seq_kv_len, const int* __restrict__ page_indptr,
+                        const int* __restrict__ page_ids, const float* __restrict__ sinks, int nh, int nkv, int head_tiles,
+                        int ps, float scale, float softcap, int window, int num_pages, int* __restrict__ status) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* bufs = reinterpret_cast<bf16*>(smem_raw);
+  trigger_dependents();
+  const int s = blockIdx.x;
+  if (seq_q_len[s] != 1) return;
+  grid_dependency_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int group = nh / nkv;
+  const int kvh = blockIdx.y / head_tiles, g0 = (blockIdx.y - kvh * head_tiles) * 16;
+  const int gn = min(16, group - g0);
+  const int tok = seq_q_start[s];
+  const int p = seq_kv_len[s] - 1;
+  const int* table = page_ids + page_indptr[s];
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+  const int k_lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+
+  uint32_t qf[KSTEPS][4];
+  int lim_lo[2] = {k_lo, k_lo}, lim_hi[2] = {p, p};
+  float m[2], l[2];
+#pragma unroll
+  for (int hh = 0; hh < 2; hh++) {
+    const int r = g + hh * 8;
+    const bool live = r < gn;
+    const int head = kvh * group + g0 + (live ? r : 0);
+    const bf16* qrow = q + ((size_t)tok * nh + head) * QK;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ks++) {
+      qf[ks][hh] = live ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t) : 0u;
+      qf[ks][hh + 2] = live ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t) : 0u;
+    }
+    m[hh] = sinks ? sinks[head] * LOG2E : NEG_BIG;
+    l[hh] = (sinks && warp == 0 && t == 0) ? 1.f : 0.f;  // the sink counts once: in the first warp's sums
+  }
+  float o[VT][4];
+#pragma unroll
+  for (int vt = 0; vt < VT; vt++) o[vt][0] = o[vt][1] = o[vt][2] = o[vt][3] = 0.f;
+
+  const int n_tiles = (p - k_lo) / KT + 1;
+  bool bad = false;
+  stage_tile(bufs, cache, table, k_lo, k_lo, p, kvh, nkv, ps, num_pages, bad, tid);
+  cp_async_commit();
+  for (int it = 0; it < n_tiles; it++) {
+    bf16* cur = bufs + (it & 1) * KT * RS;
+    if (it + 1 < n_tiles) {
+      stage_tile(bufs + ((it + 1) & 1) * KT * RS, cache, table, k_lo + (it + 1) * KT, k_lo, p, kvh, nkv, ps, num_pages, bad, tid);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int key0 = k_lo + it * KT + warp * 16;
+    if (key0 <= p) attend<2>(cur, warp * 16, key0, qf, o, m, l, lim_lo, lim_hi, scale, softcap, inv_cap, lane);
+    __syncthreads();
+  }
+  report_bad_page(bad, status);
+#pragma unroll
+  for (int hh = 0; hh < 2; hh++) {
+    l[hh] += __shfl_xor_sync(0xffffffffu, l[hh], 1);
+    l[hh] += __shfl_xor_sync(0xffffffffu, l[hh], 2);
+  }
+  // the four warps' partial results through shared memory (the tile buffers are free now)
+  constexpr int SO = VD + 8;
+  static_assert((size_t)(4 * 16 * SO + 4 * 16 * 2) * sizeof(float) <= TC_SMEM, "the merge scratch fits the tile buffers");
+  float* so = reinterpret_cast<float*>(smem_raw);
+  float* sml = so + 4 * 16 * SO;
+#pragma unroll
+  for (int vt = 0; vt < VT; vt++) {
+    float* b = so + (warp * 16 + g) * SO + vt * 8 + 2 * t;
+    *reinterpret_cast<float2*>(b) = make_float2(o[vt][0], o[vt][1]);
+    *reinterpret_cast<float2*>(b + 8 * SO) = make_float2(o[vt][2], o[vt][3]);
+  }
+  if (t == 0) {
+    sml[(warp * 16 + g) * 2] = m[0];
+    sml[(warp * 16 + g) * 2 + 1] = l[0];
+    sml[(warp * 16 + g + 8) * 2] = m[1];
+    sml[(warp * 16 + g + 8) * 2 + 1] = l[1];
+  }
+  __syncthreads();
+  for (int idx = tid; idx < gn * VD; idx += 128) {
+    const int r = idx / VD, d = idx - r * VD;
+    float mm = NEG_BIG;
+#pragma unroll
+    for (int w = 0; w < 4; w++) mm = fmaxf(mm, sml[(w * 16 + r) * 2]);
+    float acc = 0.f, ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+      const float f = exp2f(sml[(w * 16 + r) * 2] - mm);
+      acc += f * so[(w * 16 + r) * SO + d];
+      ll += f * sml[(w * 16 + r) * 2 + 1];
+    }
+    out[((size_t)tok * nh + kvh * group + g0 + r) * VD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+  }
+}
+
+}  // namespace
+
+// Attention of every token of the step (bfloat16): requests with one token through attn_sink_single, longer portions
+// through attn_sink_tiles.  n_tokens and n_seqs size the grids; the blocks read the rest from the request table.
+TKB_EXPORT int tkb_attn_sink_tc_bf16(const void* q, void* out, const void* cache, const int* seq_q_start,
+                                     const int* seq_q_len, const int* seq_kv_len, const int* page_indptr,
+                                     const int* page_ids, int n_tokens, int n_seqs, int portions, int singles,
+                                     const float* sinks, int nh, int nkv, int page_size, float scale, float softcap,
+                                     int window, int num_pages, int* status, void* st) {
+  if (n_tokens <= 0 || n_seqs <= 0) return 0;
+  if (nkv <= 0 || nh % nkv != 0 || page_size <= 0) return -2;
+  const int head_tiles = (nh / nkv + 15) / 16;
+  if (nh > 65535 || nkv * head_tiles > 65535) return -3;
+  if (TC_SMEM > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(attn_sink_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_sink_single_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
+    if (e != cudaSuccess) return (int)e;
+  }
+  int rc = 0;
+  if (singles)
+    rc = launch_pdl(attn_sink_single_kernel, dim3(n_seqs, nkv * head_tiles), dim3(128), TC_SMEM, (cudaStream_t)st,
+                    (const bf16*)q, (bf16*)out, (const bf16*)cache, seq_q_start, seq_q_len, seq_kv_len, page_indptr,
+                    page_ids, sinks, nh, nkv, head_tiles, page_size, scale, softcap, window, num_pages, status);
+  if (rc != 0 || !portions) return rc;
+  const int tiles = n_tokens / KT + n_seqs;  // no step of this shape has more 64-query tiles
+  return launch_pdl(attn_sink_tiles_kernel, dim3(tiles, nh), dim3(128), TC_SMEM, (cudaStream_t)st, (const bf16*)q,
+                    (bf16*)out, (const bf16*)cache, seq_q_start, seq_q_len, seq_kv_len, page_indptr, page_ids, n_seqs,
+                    sinks, nh, nkv, page_size, scale, softcap, window, num_pages, status);
+}
+#endif  // tensor-core sizes
+TKB_EXPORT int tkb_attn_sink_has_tc() {
+#ifdef TKB_SINK_TC
+  return 1;
+#else
+  return 0;
+#endif
+}

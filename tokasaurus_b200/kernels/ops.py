@@ -1166,6 +1166,32 @@ def attn_sink(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, token_seq
         c_float(softcap or 0.0), c_int(window or 0), c_int(cache.shape[0]), _ptr(status), _stream()), "attn_sink")
 
 
+def can_use_attn_sink_tc(dtype: torch.dtype, dim: int, vdim: int) -> bool:
+    """The tensor-core kernels of csrc/attention_sink.cu take bfloat16 rows whose key and value sizes are multiples of 16."""
+    return dtype == torch.bfloat16 and dim % 16 == 0 and vdim % 16 == 0 and dim + vdim <= 512
+
+
+def attn_sink_tc(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, seq_q_start: torch.Tensor, seq_q_len: torch.Tensor,
+                 seq_kv_len: torch.Tensor, page_indptr: torch.Tensor, page_ids: torch.Tensor, n_seqs: int,
+                 sinks: torch.Tensor | None, n_heads: int, n_kv_heads: int, dim: int, vdim: int, page_size: int, scale: float,
+                 softcap: float | None, window: int | None, status: torch.Tensor, portions: bool = True,
+                 singles: bool = True) -> None:
+    """Attention of every token of the step on the tensor cores (bfloat16): out [T, heads * vdim].  ``portions`` /
+    ``singles``: whether the step can hold requests with several tokens / with one (a kernel each)."""
+    _need_cuda(q, out, cache, seq_q_start, seq_q_len, seq_kv_len, page_indptr, page_ids, sinks, status)
+    T = q.shape[0]
+    _need(can_use_attn_sink_tc(cache.dtype, dim, vdim), "attn_sink_tc: bfloat16 rows, key and value sizes multiples of 16")
+    _need(q.is_contiguous() and q.shape[1] == n_heads * dim and q.dtype == cache.dtype and out.dtype == cache.dtype
+          and out.is_contiguous() and tuple(out.shape) == (T, n_heads * vdim), "attn_sink_tc: q and out")
+    _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (n_kv_heads, page_size, dim + vdim), "attn_sink_tc: cache rows")
+    _need(sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == n_heads), "attn_sink_tc: sinks float32 [heads]")
+    _check(_fn(_libs.get("attention_sink.cu", **sink_attention_defines(dim, vdim)), "tkb_attn_sink_tc_bf16")(
+        _ptr(q), _ptr(out), _ptr(cache), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(page_indptr),
+        _ptr(page_ids), c_int(T), c_int(n_seqs), c_int(1 if portions else 0), c_int(1 if singles else 0), _ptr(sinks),
+        c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale), c_float(softcap or 0.0), c_int(window or 0),
+        c_int(cache.shape[0]), _ptr(status), _stream()), "attn_sink_tc")
+
+
 def prepare_modules(modules) -> None:
     """Build and load the listed (source file, constants) modules."""
     for source, defines in modules:

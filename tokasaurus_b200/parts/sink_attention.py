@@ -11,7 +11,9 @@ takes part in the denominator only.  The output projection may carry a bias (``o
 
 A token's key and value of one key/value head are cached side by side as one row [k | v] (one plane): rows
 ``[page, kv head, slot, dim + vdim]``.  The projections are one product with a float32 result; biases, the unit norms,
-scores, weights and sums are float32.
+scores, weights and sums are float32.  In float32, and for head sizes that are no multiples of 16, one FP32-pipe kernel
+serves every token; in bfloat16 otherwise the tensor-core kernels of csrc/attention_sink.cu do (weights rounded to
+bfloat16 for their product with the values, as in the framework's other attention kernels).
 """
 
 from __future__ import annotations
@@ -79,6 +81,18 @@ class SinkAttention(Mixer):
         q = torch.empty((T, H * d), dtype=h.dtype, device=h.device)
         ops.sink_attn_prep(qkv, self.qkv_bias, self.unit_norm, self.norm_eps, q, cache.k, ctx.positions, ctx.token_seq,
                            tables.indptr, tables.page_ids, H, G, d, e, cache.page_size, cache.writable, ctx.status)
+        if ops.can_use_attn_sink_tc(h.dtype, d, e):
+            # bfloat16: every token on the tensor cores (single tokens and portions by a kernel each); wanted rows are
+            # cut out afterwards
+            attn = torch.empty((T, H * e), dtype=h.dtype, device=h.device)
+            ops.attn_sink_tc(q, attn, cache.k, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, tables.indptr,
+                             tables.page_ids, ctx.n_seqs, self.sinks, H, G, d, e, cache.page_size, self.scale, self.softcap,
+                             self.window, ctx.status, portions=not ctx.single_token_step)
+            if out_rows is not None:
+                cut = torch.empty((out_rows.numel(), H * e), dtype=h.dtype, device=h.device)
+                ops.gather_rows(attn, out_rows, cut)
+                attn = cut
+            return ops.linear(attn, self.w_o, out_dtype=torch.float32)
         n_rows = T if out_rows is None else out_rows.numel()
         attn = torch.empty((n_rows, H * e), dtype=h.dtype, device=h.device)
         ops.attn_sink(q, attn, cache.k, ctx.token_seq, ctx.positions, tables.indptr, tables.page_ids, out_rows, n_rows,
