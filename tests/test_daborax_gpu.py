@@ -191,11 +191,16 @@ def test_decay_walk_in_portions(ops, heads, groups, dim, vdim):
             T = sum(ql)
             out = torch.empty(T, heads * vdim, device=DEV)
             if form == "per_head":
-                ops.decay_walk(cat(q), cat(k), cat(v), 1, None, decay.to(DEV), None, state, out, i32([slots[s] for s in live]),
-                               i32(qs), i32(ql), len(live), heads, dim, vdim, True, defines)
+                # q, k and v as column slices of one tensor with something behind them, SiLU applied in place
+                wide = torch.cat([cat(q), cat(k), cat(v), torch.full((T, 3), 9.0, device=DEV)], dim=1)
+                ops.silu_cols(wide, wide.shape[1] - 3, defines)
+                assert float((wide[:, -3:] - 9.0).abs().max()) == 0.0
+                ops.decay_walk(wide[:, :G * dim], wide[:, G * dim:2 * G * dim], wide[:, 2 * G * dim:-3], 1, None, decay.to(DEV),
+                               None, state, out, i32([slots[s] for s in live]), i32(qs), i32(ql), len(live), heads, dim, vdim,
+                               defines)
             else:
                 ops.decay_walk(cat(q), cat(k), cat(v), heads // groups, cat(dd), None, skip.to(DEV), state, out,
-                               i32([slots[s] for s in live]), i32(qs), i32(ql), len(live), heads, dim, vdim, False, defines)
+                               i32([slots[s] for s in live]), i32(qs), i32(ql), len(live), heads, dim, vdim, defines)
             for s, a, n in zip(live, qs, ql):
                 got[s].append(out[a:a + n].cpu())
                 at[s] += n

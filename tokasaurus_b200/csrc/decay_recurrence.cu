@@ -3,8 +3,8 @@
 //     S_t = a_t S_(t-1) + (c_t k_t) v_t^T,        o_t = S_t^T q_t + D v_t
 //
 // (S is dim x vdim; k_t, q_t have dim entries, v_t has vdim).  Two mixers are instances of it:
-//   * decayed linear attention: a_t = lambda_head (a constant), c_t = 1, D = 0, q, k, v = silu of the projections, one
-//     q and k per head;
+//   * decayed linear attention: a_t = lambda_head (a constant), c_t = 1, D = 0, q, k, v = silu of the projections
+//     (silu_cols, in place), one q and k per head;
 //   * the selective state space (state-space duality form): a_t = exp(-exp(A_head) dt_t), c_t = dt_t, k = B, q = C
 //     shared by the heads of a group, v = x, D a number per head; x, B and C come out of a causal convolution over
 //     time with bias and SiLU, dt_t = softplus(dt_raw + dt_bias).
@@ -16,12 +16,13 @@
 // every token has read them), decay_walk (the recurrence).
 //
 // The walk: one block owns some columns of the state of one (request, head) and goes over the request's tokens of
-// this step in order.  Eight threads share a column j of S (dims lane, lane + 8, ...): a step is DPT multiply-adds
-// and a three-step shuffle sum a thread.  Tokens are staged in chunks of 16 in shared memory.  With few requests and
-// many tokens a head's columns are spread over as many blocks as fill the SMs twice: the chain over the tokens is
-// what takes the time.
+// this step in order.  Eight threads share a column j of S (lane L holds dims L * DPT ..): a step is 2 DPT multiply-adds
+// and a three-step shuffle sum a thread.  Tokens come in chunks of 16 by cp.async, one chunk ahead, into rows whose
+// padding keeps the lanes' 16-byte reads on different banks.  With few requests and many tokens a head's columns are
+// spread over as many blocks as fill the SMs four times: the chain over the tokens is what takes the time, so it is
+// made as thin as it gets (four columns, one warp).  Activations of q, k and v are applied beforehand, once.
 //
-// Compile with -DTKB_DR_DPT=<ceil(dim / 8)> and -DTKB_DR_CPT=<ceil(vdim / 128)>.
+// Compile with -DTKB_DR_DPT=<dims a lane: 4 * ceil(dim / 32)> and -DTKB_DR_CPT=<ceil(vdim / 128)>.
 #include "common.cuh"
 
 #ifndef TKB_DR_DPT
@@ -36,9 +37,9 @@ using namespace tkb;
 namespace {
 
 constexpr int DPT = TKB_DR_DPT;
+static_assert(DPT % 4 == 0 && DPT >= 4, "dims a lane: a multiple of 4");
 constexpr int CPT = TKB_DR_CPT;
 constexpr int LANES = 8;
-constexpr int DIM_PAD = DPT * LANES;
 constexpr int CHUNK = 16;
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
@@ -99,24 +100,43 @@ conv_carry_kernel(const float* __restrict__ proj, int stride, int xbc_off, int C
   }
 }
 
-template <bool ACT>
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_addr(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// SiLU in place on `ncols` columns of float32 rows (the projections of a mixer whose q, k and v pass through it): done
+// once for all tokens, not by every block that walks over them.
+__global__ void silu_cols_kernel(float* __restrict__ x, int stride, int ncols) {
+  trigger_dependents();
+  grid_dependency_wait();
+  float* row = x + (size_t)blockIdx.x * stride;
+  for (int c = threadIdx.x; c < ncols; c += blockDim.x) row[c] = silu_f(row[c]);
+}
+
+// Shared memory of the walk, per buffer: q and k rows of QROW floats (lane L's DPT dims at L * (DPT + 4): the padding
+// keeps 16-byte reads of the eight lanes on different banks), v and the outputs at `cols` floats a token, decay and key
+// scale a float a token each.
+constexpr int QROW = LANES * (DPT + 4);
+
 __global__ void __launch_bounds__(1024)
 decay_walk_kernel(const float* __restrict__ q, int q_stride, const float* __restrict__ k, int k_stride, int qk_div,
                   const float* __restrict__ v, int v_stride, const float* __restrict__ dt_dec,
                   const float* __restrict__ decay_head, const float* __restrict__ skip, float* __restrict__ state,
                   long long slot_stride, float* __restrict__ out, const int* __restrict__ seq_slot,
                   const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len, int heads, int dim, int vdim,
-                  int write_state, int cols_per_block) {
-  extern __shared__ float smem[];
+                  int write_state, int cols_per_block, int vec_qk, int vec_v, int vec_s, int defer) {
+  extern __shared__ __align__(16) float smem[];
   const int cols = min(cols_per_block, vdim);
-  float* qs = smem;                       // [CHUNK][DIM_PAD]
-  float* ks = qs + CHUNK * DIM_PAD;       // [CHUNK][DIM_PAD]
-  float* vs = ks + CHUNK * DIM_PAD;       // [CHUNK][cols]
-  float* os = vs + CHUNK * cols;          // [CHUNK][cols]
-  float* as = os + CHUNK * cols;          // [CHUNK] decay
-  float* cs = as + CHUNK;                 // [CHUNK] key scale
+  const int cols4 = (cols + 3) & ~3;
+  const int buf_floats = CHUNK * (2 * QROW + cols4 + 2);
+  float* os = smem + 2 * buf_floats;  // [CHUNK][cols]
   trigger_dependents();
-  grid_dependency_wait();
   const int s = blockIdx.x, head = blockIdx.y;
   const int n = seq_q_len[s];
   if (n <= 0) return;
@@ -126,17 +146,32 @@ decay_walk_kernel(const float* __restrict__ q, int q_stride, const float* __rest
   const int col_begin = blockIdx.z * cols_per_block;
   const int col_end = min(vdim, col_begin + cols_per_block);
   if (col_begin >= col_end) return;
+  const int ncols = col_end - col_begin;
   const int lc0 = tid / LANES;  // local column of the first pass
+  // dims beyond `dim` of the last lanes are read: zero the buffers once if there are any (the copies never touch them)
+  if (dim < LANES * DPT)
+    for (int idx = tid; idx < 2 * buf_floats; idx += blockDim.x) smem[idx] = 0.f;
+  grid_dependency_wait();
   float* st = state + (size_t)seq_slot[s] * slot_stride + (size_t)head * vdim * dim;
 
   float S[CPT][DPT];
 #pragma unroll
   for (int c = 0; c < CPT; c++) {
     const int j = col_begin + lc0 + c * cols_per_pass;
+    if (vec_s) {
 #pragma unroll
-    for (int i = 0; i < DPT; i++) {
-      const int d = lane + LANES * i;
-      S[c][i] = (j < col_end && d < dim) ? st[(size_t)j * dim + d] : 0.f;
+      for (int i = 0; i < DPT; i += 4) {
+        const int d = lane * DPT + i;
+        const float4 x = (j < col_end && d < dim) ? *reinterpret_cast<const float4*>(st + (size_t)j * dim + d)
+                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+        S[c][i] = x.x; S[c][i + 1] = x.y; S[c][i + 2] = x.z; S[c][i + 3] = x.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < DPT; i++) {
+        const int d = lane * DPT + i;
+        S[c][i] = (j < col_end && d < dim) ? st[(size_t)j * dim + d] : 0.f;
+      }
     }
   }
   const float* qh = q + (size_t)(head / qk_div) * dim;
@@ -144,84 +179,150 @@ decay_walk_kernel(const float* __restrict__ q, int q_stride, const float* __rest
   const float* vh = v + (size_t)head * vdim + col_begin;
   const float a_const = decay_head ? decay_head[head] : 1.f;
   const float d_skip = skip ? skip[head] : 0.f;
-  const int ncols = col_end - col_begin;
+  __syncthreads();  // the zeros are in place before the first copies land
 
-  for (int t0 = 0; t0 < n; t0 += CHUNK) {
+  auto stage = [&](int t0, int b) {
+    float* qs = smem + b * buf_floats;
+    float* ks = qs + CHUNK * QROW;
+    float* vs = ks + CHUNK * QROW;
+    float* as = vs + CHUNK * cols4;
+    float* cs = as + CHUNK;
     const int nt = min(CHUNK, n - t0);
-    __syncthreads();  // the chunk before is out of shared memory
-    for (int idx = tid; idx < nt * DIM_PAD; idx += blockDim.x) {
-      const int t = idx / DIM_PAD, d = idx - t * DIM_PAD;
-      float qv = 0.f, kv = 0.f;
-      if (d < dim) {
-        qv = qh[(size_t)(start + t0 + t) * q_stride + d];
-        kv = kh[(size_t)(start + t0 + t) * k_stride + d];
-        if (ACT) { qv = silu_f(qv); kv = silu_f(kv); }
+    if (vec_qk) {
+      const int d4n = dim >> 2;
+      for (int idx = tid; idx < nt * d4n; idx += blockDim.x) {
+        const int t = idx / d4n, d = (idx - t * d4n) * 4;
+        const int at = t * QROW + (d / DPT) * (DPT + 4) + (d % DPT);
+        cp_async16(qs + at, qh + (size_t)(start + t0 + t) * q_stride + d);
+        cp_async16(ks + at, kh + (size_t)(start + t0 + t) * k_stride + d);
       }
-      qs[idx] = qv;
-      ks[idx] = kv;
+    } else {
+      for (int idx = tid; idx < nt * dim; idx += blockDim.x) {
+        const int t = idx / dim, d = idx - t * dim;
+        const int at = t * QROW + (d / DPT) * (DPT + 4) + (d % DPT);
+        cp_async4(qs + at, qh + (size_t)(start + t0 + t) * q_stride + d);
+        cp_async4(ks + at, kh + (size_t)(start + t0 + t) * k_stride + d);
+      }
     }
-    for (int idx = tid; idx < nt * ncols; idx += blockDim.x) {
-      const int t = idx / ncols, j = idx - t * ncols;
-      float vv = vh[(size_t)(start + t0 + t) * v_stride + j];
-      if (ACT) vv = silu_f(vv);
-      vs[t * cols + j] = vv;
+    if (vec_v && (ncols & 3) == 0) {
+      const int c4n = ncols >> 2;
+      for (int idx = tid; idx < nt * c4n; idx += blockDim.x) {
+        const int t = idx / c4n, j = (idx - t * c4n) * 4;
+        cp_async16(vs + t * cols4 + j, vh + (size_t)(start + t0 + t) * v_stride + j);
+      }
+    } else {
+      for (int idx = tid; idx < nt * ncols; idx += blockDim.x) {
+        const int t = idx / ncols, j = idx - t * ncols;
+        cp_async4(vs + t * cols4 + j, vh + (size_t)(start + t0 + t) * v_stride + j);
+      }
     }
-    if (tid < nt) {
-      as[tid] = dt_dec ? dt_dec[(size_t)(start + t0 + tid) * 2 * heads + heads + head] : a_const;
-      cs[tid] = dt_dec ? dt_dec[(size_t)(start + t0 + tid) * 2 * heads + head] : 1.f;
+    if (dt_dec != nullptr) {
+      for (int t = tid; t < nt; t += blockDim.x) {
+        cp_async4(cs + t, dt_dec + (size_t)(start + t0 + t) * 2 * heads + head);
+        cp_async4(as + t, dt_dec + (size_t)(start + t0 + t) * 2 * heads + heads + head);
+      }
+    }
+    cp_async_commit();
+  };
+
+  stage(0, 0);
+  int b = 0;
+  for (int t0 = 0; t0 < n; t0 += CHUNK, b ^= 1) {
+    const int nt = min(CHUNK, n - t0);
+    if (t0 + CHUNK < n) {
+      stage(t0 + CHUNK, b ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
     __syncthreads();
+    const float* qs = smem + b * buf_floats;
+    const float* ks = qs + CHUNK * QROW;
+    const float* vs = ks + CHUNK * QROW;
+    const float* as = vs + CHUNK * cols4;
+    const float* cs = as + CHUNK;
+#pragma unroll 2
     for (int t = 0; t < nt; t++) {
-      const float a = as[t], ck = cs[t];
-      const float* qt = qs + t * DIM_PAD;
-      const float* kt = ks + t * DIM_PAD;
+      const float a = dt_dec ? as[t] : a_const, ck = dt_dec ? cs[t] : 1.f;
+      const float4* q4 = reinterpret_cast<const float4*>(qs + t * QROW + lane * (DPT + 4));
+      const float4* k4 = reinterpret_cast<const float4*>(ks + t * QROW + lane * (DPT + 4));
 #pragma unroll
       for (int c = 0; c < CPT; c++) {
         const int lc = lc0 + c * cols_per_pass;
-        const float vj = lc < ncols ? vs[t * cols + lc] : 0.f;
-        float acc = 0.f;
+        const float vj = lc < ncols ? vs[t * cols4 + lc] : 0.f;
+        const float cv = ck * vj;
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-        for (int i = 0; i < DPT; i++) {
-          const int d = lane + LANES * i;
-          S[c][i] = fmaf(a, S[c][i], (kt[d] * ck) * vj);
-          acc = fmaf(S[c][i], qt[d], acc);
+        for (int i = 0; i < DPT / 4; i++) {
+          const float4 qq = q4[i], kk = k4[i];
+          S[c][4 * i + 0] = fmaf(a, S[c][4 * i + 0], kk.x * cv);
+          S[c][4 * i + 1] = fmaf(a, S[c][4 * i + 1], kk.y * cv);
+          S[c][4 * i + 2] = fmaf(a, S[c][4 * i + 2], kk.z * cv);
+          S[c][4 * i + 3] = fmaf(a, S[c][4 * i + 3], kk.w * cv);
+          a0 = fmaf(S[c][4 * i + 0], qq.x, a0);
+          a1 = fmaf(S[c][4 * i + 1], qq.y, a1);
+          a2 = fmaf(S[c][4 * i + 2], qq.z, a2);
+          a3 = fmaf(S[c][4 * i + 3], qq.w, a3);
         }
-        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-        if (lane == 0 && lc < ncols) os[t * cols + lc] = fmaf(d_skip, vj, acc);
+        float acc = (a0 + a1) + (a2 + a3);
+        if (defer) {
+          // few columns a block (one or two warps): a warp that waited for three shuffles a token would have nothing
+          // else to issue; the lanes' shares go to shared memory and are added up after the chunk
+          if (lc < ncols) os[(t * cols + lc) * LANES + lane] = lane == 0 ? fmaf(d_skip, vj, acc) : acc;
+        } else {
+          acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+          acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+          acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+          if (lane == 0 && lc < ncols) os[t * cols + lc] = fmaf(d_skip, vj, acc);
+        }
       }
     }
-    __syncthreads();
+    __syncthreads();  // the chunk's outputs are complete; its buffer may be filled again (by the stage after next)
     for (int idx = tid; idx < nt * ncols; idx += blockDim.x) {
       const int t = idx / ncols, j = idx - t * ncols;
-      out[(size_t)(start + t0 + t) * heads * vdim + (size_t)head * vdim + col_begin + j] = os[t * cols + j];
+      float o;
+      if (defer) {
+        const float4 x = *reinterpret_cast<const float4*>(os + (t * cols + j) * LANES);
+        const float4 y = *reinterpret_cast<const float4*>(os + (t * cols + j) * LANES + 4);
+        o = ((x.x + x.y) + (x.z + x.w)) + ((y.x + y.y) + (y.z + y.w));
+      } else {
+        o = os[t * cols + j];
+      }
+      out[(size_t)(start + t0 + t) * heads * vdim + (size_t)head * vdim + col_begin + j] = o;
     }
   }
   if (write_state) {
 #pragma unroll
     for (int c = 0; c < CPT; c++) {
       const int j = col_begin + lc0 + c * cols_per_pass;
+      if (vec_s) {
 #pragma unroll
-      for (int i = 0; i < DPT; i++) {
-        const int d = lane + LANES * i;
-        if (j < col_end && d < dim) st[(size_t)j * dim + d] = S[c][i];
+        for (int i = 0; i < DPT; i += 4) {
+          const int d = lane * DPT + i;
+          if (j < col_end && d < dim)
+            *reinterpret_cast<float4*>(st + (size_t)j * dim + d) = make_float4(S[c][i], S[c][i + 1], S[c][i + 2], S[c][i + 3]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < DPT; i++) {
+          const int d = lane * DPT + i;
+          if (j < col_end && d < dim) st[(size_t)j * dim + d] = S[c][i];
+        }
       }
     }
   }
 }
 
-template <bool ACT>
 int walk_launch(const float* q, int q_stride, const float* k, int k_stride, int qk_div, const float* v, int v_stride,
                 const float* dt_dec, const float* decay_head, const float* skip, float* state, long long slot_stride,
                 float* out, const int* seq_slot, const int* seq_q_start, const int* seq_q_len, int n_seqs, int n_tokens,
                 int heads, int dim, int vdim, int write_state, cudaStream_t st) {
   if (n_seqs <= 0 || n_tokens <= 0) return 0;
-  if (dim <= 0 || dim > DIM_PAD || vdim <= 0 || vdim > CPT * 128 || heads <= 0 || qk_div <= 0) return -2;
+  if (dim <= 0 || dim > DPT * LANES || vdim <= 0 || vdim > CPT * 128 || heads <= 0 || qk_div <= 0) return -2;
   if (heads > 65535) return -3;
   int cols_per_block = vdim;
-  if (n_tokens > n_seqs) {  // portions: spread a head's columns over blocks until the SMs are filled twice
-    const int want = 2 * sm_count();
+  if (n_tokens > n_seqs) {  // portions: spread a head's columns over blocks until the SMs are filled four times
+    const int want = 4 * sm_count();
     const int have = n_seqs * heads;
     const int splits = have >= want ? 1 : (want + have - 1) / have;
     cols_per_block = (vdim + splits - 1) / splits;
@@ -233,14 +334,20 @@ int walk_launch(const float* q, int q_stride, const float* k, int k_stride, int 
   if (per_pass > 128) per_pass = 128;
   int threads = ((per_pass * LANES + 31) / 32) * 32;
   const int cols = cols_per_block < vdim ? cols_per_block : vdim;
-  const size_t smem = (size_t)(CHUNK * (2 * DIM_PAD + 2 * cols) + 2 * CHUNK) * sizeof(float);
+  const int cols4 = (cols + 3) & ~3;
+  const int defer = cols <= 16;
+  const size_t smem = (size_t)(2 * CHUNK * (2 * QROW + cols4 + 2) + CHUNK * cols * (defer ? LANES : 1)) * sizeof(float);
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(decay_walk_kernel<ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(decay_walk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return launch_pdl(decay_walk_kernel<ACT>, dim3(n_seqs, heads, splits), dim3(threads), smem, st, q, q_stride, k,
-                    k_stride, qk_div, v, v_stride, dt_dec, decay_head, skip, state, slot_stride, out, seq_slot,
-                    seq_q_start, seq_q_len, heads, dim, vdim, write_state, cols_per_block);
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const int vec_qk = dim % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 && al16(q) && al16(k);
+  const int vec_v = vdim % 4 == 0 && v_stride % 4 == 0 && cols_per_block % 4 == 0 && al16(v);
+  const int vec_s = dim % 4 == 0 && slot_stride % 4 == 0 && al16(state);
+  return launch_pdl(decay_walk_kernel, dim3(n_seqs, heads, splits), dim3(threads), smem, st, q, q_stride, k, k_stride,
+                    qk_div, v, v_stride, dt_dec, decay_head, skip, state, slot_stride, out, seq_slot, seq_q_start,
+                    seq_q_len, heads, dim, vdim, write_state, cols_per_block, vec_qk, vec_v, vec_s, defer);
 }
 
 }  // namespace
@@ -262,18 +369,20 @@ TKB_EXPORT int tkb_ssm_prep(const float* proj, int stride, int xbc_off, int C, i
                     taps, state, slot_stride, carry_off, seq_slot, seq_q_start, seq_q_len);
 }
 
-// act != 0: q, k and v pass through SiLU on their way in.  dt_dec: float32 [T, 2 * heads] (key scale, then decay) or
-// null, then decay_head [heads] is the decay and the key scale is 1.  skip: [heads] or null.
+// dt_dec: float32 [T, 2 * heads] (key scale, then decay) or null, then decay_head [heads] is the decay and the key
+// scale is 1.  skip: [heads] or null.
 TKB_EXPORT int tkb_decay_walk(const float* q, int q_stride, const float* k, int k_stride, int qk_div, const float* v,
                               int v_stride, const float* dt_dec, const float* decay_head, const float* skip,
                               float* state, long long slot_stride, float* out, const int* seq_slot,
                               const int* seq_q_start, const int* seq_q_len, int n_seqs, int n_tokens, int heads, int dim,
-                              int vdim, int write_state, int act, void* st) {
-  if (act)
-    return walk_launch<true>(q, q_stride, k, k_stride, qk_div, v, v_stride, dt_dec, decay_head, skip, state, slot_stride,
-                             out, seq_slot, seq_q_start, seq_q_len, n_seqs, n_tokens, heads, dim, vdim, write_state,
-                             (cudaStream_t)st);
-  return walk_launch<false>(q, q_stride, k, k_stride, qk_div, v, v_stride, dt_dec, decay_head, skip, state, slot_stride,
-                            out, seq_slot, seq_q_start, seq_q_len, n_seqs, n_tokens, heads, dim, vdim, write_state,
-                            (cudaStream_t)st);
+                              int vdim, int write_state, void* st) {
+  return walk_launch(q, q_stride, k, k_stride, qk_div, v, v_stride, dt_dec, decay_head, skip, state, slot_stride, out,
+                     seq_slot, seq_q_start, seq_q_len, n_seqs, n_tokens, heads, dim, vdim, write_state, (cudaStream_t)st);
+}
+
+TKB_EXPORT int tkb_silu_cols(float* x, int stride, int ncols, int rows, void* st) {
+  if (rows <= 0 || ncols <= 0) return 0;
+  int threads = 32;
+  while (threads < ncols / 4 && threads < 512) threads <<= 1;
+  return launch_pdl(silu_cols_kernel, dim3(rows), dim3(threads), 0, (cudaStream_t)st, x, stride, ncols);
 }

@@ -1063,7 +1063,7 @@ def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, 
 # The recurrence with one decay a head and token (csrc/decay_recurrence.cu)
 def decay_recurrence_defines(dim: int, vdim: int) -> dict:
     _need(0 < dim <= 256 and 0 < vdim <= 512, f"decay recurrence: heads up to 256 x 512, not {dim} x {vdim}")
-    return dict(TKB_DR_DPT=(dim + 7) // 8, TKB_DR_CPT=(vdim + 127) // 128)
+    return dict(TKB_DR_DPT=4 * ((dim + 31) // 32), TKB_DR_CPT=(vdim + 127) // 128)
 
 
 def ssm_prep(proj: torch.Tensor, xbc_off: int, channels: int, conv_w: torch.Tensor, conv_b: torch.Tensor | None,
@@ -1098,10 +1098,10 @@ def ssm_prep(proj: torch.Tensor, xbc_off: int, channels: int, conv_w: torch.Tens
 def decay_walk(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads_per_qk: int, dt_dec: torch.Tensor | None,
                decay_head: torch.Tensor | None, skip: torch.Tensor | None, state: torch.Tensor, out: torch.Tensor,
                seq_slot: torch.Tensor, seq_q_start: torch.Tensor, seq_q_len: torch.Tensor, n_seqs: int, heads: int,
-               dim: int, vdim: int, act: bool, defines: dict, write_state: bool = True) -> None:
+               dim: int, vdim: int, defines: dict, write_state: bool = True) -> None:
     """S_t = a_t S_(t-1) + (c_t k_t) v_t^T, o_t = S_t^T q_t + skip * v_t over each request's tokens.  q, k [T, . * dim]
-    and v [T, heads * vdim] are float32 (column slices allowed); head h reads q and k number h // heads_per_qk;
-    ``act``: all three pass through SiLU.  ``dt_dec`` [T, 2 heads] = (c, a) per token, or ``decay_head`` [heads] with
+    and v [T, heads * vdim] are float32 (column slices allowed); head h reads q and k number h // heads_per_qk.
+    ``dt_dec`` [T, 2 heads] = (c, a) per token, or ``decay_head`` [heads] with
     c = 1.  state float32 [slots, n], S^T of the heads first: [heads, vdim, dim]; out float32 [T, heads * vdim]."""
     _need_cuda(q, k, v, dt_dec, decay_head, skip, state, out, seq_slot, seq_q_start, seq_q_len)
     T = q.shape[0]
@@ -1121,7 +1121,15 @@ def decay_walk(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads_per_qk: 
         _ptr(q), c_int(q.stride(0)), _ptr(k), c_int(k.stride(0)), c_int(heads_per_qk), _ptr(v), c_int(v.stride(0)),
         _ptr(dt_dec), _ptr(decay_head), _ptr(skip), _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(out),
         _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), c_int(n_seqs), c_int(T), c_int(heads), c_int(dim), c_int(vdim),
-        c_int(1 if write_state else 0), c_int(1 if act else 0), _stream()), "decay_walk")
+        c_int(1 if write_state else 0), _stream()), "decay_walk")
+
+
+def silu_cols(x: torch.Tensor, ncols: int, defines: dict) -> None:
+    """SiLU in place on the first ``ncols`` columns of float32 rows."""
+    _need_cuda(x)
+    _need(x.dtype == torch.float32 and x.stride(1) == 1 and 0 <= ncols <= x.shape[1], "silu_cols: float32 rows")
+    _check(_fn(_libs.get("decay_recurrence.cu", **defines), "tkb_silu_cols")(
+        _ptr(x), c_int(x.stride(0)), c_int(ncols), c_int(x.shape[0]), _stream()), "silu_cols")
 
 
 # ---------------------------------------------------------------------------------------------

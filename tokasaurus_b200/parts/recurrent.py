@@ -111,9 +111,10 @@ class DecayedLinearAttention(Mixer):
         proj = ops.linear(h, self.w_qkvg, out_dtype=torch.float32)
         q, k = proj[:, :H * d], proj[:, H * d:2 * H * d]
         v, g = proj[:, 2 * H * d:2 * H * d + H * e], proj[:, 2 * H * d + H * e:]
+        ops.silu_cols(proj, 2 * H * d + H * e, self.defines)  # q, k and v, in place
         raw = torch.empty((T, H * e), dtype=torch.float32, device=h.device)
         ops.decay_walk(q, k, v, 1, None, self.decay_t, None, cache.state, raw, ctx.seq_slot, ctx.seq_q_start,
-                       ctx.seq_q_len, ctx.n_seqs, H, d, e, True, self.defines, cache.writable)
+                       ctx.seq_q_len, ctx.n_seqs, H, d, e, self.defines, cache.writable)
         if out_rows is not None:
             raw, g = _rows(raw, out_rows), _rows(g.contiguous(), out_rows)
         o = torch.empty(raw.shape, dtype=h.dtype, device=h.device)

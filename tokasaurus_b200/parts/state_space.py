@@ -78,7 +78,7 @@ class SelectiveStateSpace(Mixer):
         raw = torch.empty((T, inner), dtype=torch.float32, device=h.device)
         ops.decay_walk(xbc[:, inner + G * N:], xbc[:, inner:inner + G * N], xbc[:, :inner], H // G, dt_dec, None,
                        self.d_skip, cache.state, raw, ctx.seq_slot, ctx.seq_q_start, ctx.seq_q_len, ctx.n_seqs, H, N, P,
-                       False, self.defines, cache.writable)
+                       self.defines, cache.writable)
         z = proj[:, :inner]
         if out_rows is not None:
             raw, z = _rows(raw, out_rows), _rows(z.contiguous(), out_rows)
