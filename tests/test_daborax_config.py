@@ -48,8 +48,7 @@ def test_description_follows_the_configuration():
     assert names["l2.mlp.down"].shape == (96, 56)
     mods = {(src, tuple(sorted((dd or {}).items()))) for src, dd in model.kernel_modules("bfloat16")}
     assert ("attention_sink.cu", (("TKB_QK", 24), ("TKB_VD", 40))) in mods
-    assert ("decay_recurrence.cu", (("TKB_DR_CPT", 1), ("TKB_DR_DPT", 4))) in mods   # state 20 x vdim 24
-    assert ("decay_recurrence.cu", (("TKB_DR_CPT", 1), ("TKB_DR_DPT", 8))) not in mods  # dim 16 x vdim 40: the same module
+    assert ("decay_recurrence.cu", (("TKB_DR_DPT", 4), ("TKB_DR_LANES", 8))) in mods   # state 20, dim 16: five and four 16-byte pieces
     att, ssm, lin = (b.mixer for b in model.blocks)
     assert (att.scale, att.softcap, att.window) == (0.4, 8.0, 23) and lin.decay == (0.7, 0.95, 0.999)
     assert model.blocks[0].mult == 0.6 and model.embedding.scale == 3.5 and model.blocks[2].ffn.limit == 0.8

@@ -159,7 +159,7 @@ def test_convolution_step_sizes_and_carried_inputs(ops, taps):
         state[:, 11:] = 0.0
 
 
-@pytest.mark.parametrize("heads,groups,dim,vdim", [(4, 2, 24, 40), (2, 2, 64, 16), (1, 1, 7, 130), (6, 1, 128, 64), (3, 3, 10, 300)])
+@pytest.mark.parametrize("heads,groups,dim,vdim", [(4, 2, 24, 40), (2, 2, 64, 16), (1, 1, 7, 130), (6, 1, 128, 64), (3, 3, 10, 300), (2, 1, 200, 36)])
 def test_decay_walk_in_portions(ops, heads, groups, dim, vdim):
     """Both forms (a decay per head, silu on the inputs; decays and key scales per token with a skip term and shared
     q and k per group) over two requests in portions down to one token, against the whole sequences."""

@@ -16,20 +16,22 @@
 // every token has read them), decay_walk (the recurrence).
 //
 // The walk: one block owns some columns of the state of one (request, head) and goes over the request's tokens of
-// this step in order.  Eight threads share a column j of S (lane L holds dims L * DPT ..): a step is 2 DPT multiply-adds
-// and a three-step shuffle sum a thread.  Tokens come in chunks of 16 by cp.async, one chunk ahead, into rows whose
-// padding keeps the lanes' 16-byte reads on different banks.  With few requests and many tokens a head's columns are
-// spread over as many blocks as fill the SMs four times: the chain over the tokens is what takes the time, so it is
-// made as thin as it gets (four columns, one warp).  Activations of q, k and v are applied beforehand, once.
+// this step in order.  LANES threads share a column j of S (lane L holds dims 4 (L + LANES i) .. + 3): a step is 2 DPT
+// multiply-adds and a shuffle sum a thread.  A thread holds as little of the state as the head allows (four values at
+// heads of 128): a warp alone issues an instruction every four cycles (each waits for the one before), so the time
+// goes down with the number of warps, and that is the state's size over what a thread holds.  Tokens come in chunks of
+// 16 by cp.async, one chunk ahead; the lanes' shares of a chunk's outputs wait in shared memory and are added up after
+// the chunk.  Activations of q, k and v are applied beforehand, once.
 //
-// Compile with -DTKB_DR_DPT=<dims a lane: 4 * ceil(dim / 32)> and -DTKB_DR_CPT=<ceil(vdim / 128)>.
+// Compile with -DTKB_DR_LANES=<threads that share a column: the power of two from 8 to 32 nearest above dim / 4> and
+// -DTKB_DR_DPT=<dims a lane: 4 * ceil(dim / (4 * lanes))>.
 #include "common.cuh"
 
 #ifndef TKB_DR_DPT
 #error "compile with -DTKB_DR_DPT=<dims per thread>"
 #endif
-#ifndef TKB_DR_CPT
-#define TKB_DR_CPT 1
+#ifndef TKB_DR_LANES
+#error "compile with -DTKB_DR_LANES=<threads that share a column: 8, 16 or 32>"
 #endif
 
 using namespace tkb;
@@ -38,8 +40,8 @@ namespace {
 
 constexpr int DPT = TKB_DR_DPT;
 static_assert(DPT % 4 == 0 && DPT >= 4, "dims a lane: a multiple of 4");
-constexpr int CPT = TKB_DR_CPT;
-constexpr int LANES = 8;
+constexpr int LANES = TKB_DR_LANES;
+static_assert(LANES == 8 || LANES == 16 || LANES == 32, "8, 16 or 32 threads a column");
 constexpr int CHUNK = 16;
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
@@ -119,10 +121,10 @@ __global__ void silu_cols_kernel(float* __restrict__ x, int stride, int ncols) {
   for (int c = threadIdx.x; c < ncols; c += blockDim.x) row[c] = silu_f(row[c]);
 }
 
-// Shared memory of the walk, per buffer: q and k rows of QROW floats (lane L's DPT dims at L * (DPT + 4): the padding
-// keeps 16-byte reads of the eight lanes on different banks), v and the outputs at `cols` floats a token, decay and key
-// scale a float a token each.
-constexpr int QROW = LANES * (DPT + 4);
+// Shared memory of the walk, per buffer: q and k rows of QROW floats as they lie in memory (lane L reads the 16-byte
+// pieces L, L + LANES, ...: the lanes of a column read neighbouring pieces, so no bank is hit twice), v at `cols` floats
+// a token, decay and key scale a float a token each.
+constexpr int QROW = LANES * DPT;
 
 __global__ void __launch_bounds__(1024)
 decay_walk_kernel(const float* __restrict__ q, int q_stride, const float* __restrict__ k, int k_stride, int qk_div,
@@ -130,48 +132,45 @@ decay_walk_kernel(const float* __restrict__ q, int q_stride, const float* __rest
                   const float* __restrict__ decay_head, const float* __restrict__ skip, float* __restrict__ state,
                   long long slot_stride, float* __restrict__ out, const int* __restrict__ seq_slot,
                   const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len, int heads, int dim, int vdim,
-                  int write_state, int cols_per_block, int vec_qk, int vec_v, int vec_s, int defer) {
+                  int write_state, int cols_per_block, int vec_qk, int vec_v, int vec_s, int chunk) {
   extern __shared__ __align__(16) float smem[];
   const int cols = min(cols_per_block, vdim);
   const int cols4 = (cols + 3) & ~3;
-  const int buf_floats = CHUNK * (2 * QROW + cols4 + 2);
-  float* os = smem + 2 * buf_floats;  // [CHUNK][cols]
+  const int buf_floats = chunk * (2 * QROW + cols4 + 2);
+  float* os = smem + 2 * buf_floats;  // the lanes' shares of a chunk's outputs: [cols][LANES][chunk + 1]
+  const int orow = chunk + 1;         // (one float of padding: the lanes of a column write different banks)
   trigger_dependents();
   const int s = blockIdx.x, head = blockIdx.y;
   const int n = seq_q_len[s];
   if (n <= 0) return;
   const int start = seq_q_start[s];
   const int tid = threadIdx.x, lane = tid & (LANES - 1);
-  const int cols_per_pass = blockDim.x / LANES;
   const int col_begin = blockIdx.z * cols_per_block;
   const int col_end = min(vdim, col_begin + cols_per_block);
   if (col_begin >= col_end) return;
   const int ncols = col_end - col_begin;
-  const int lc0 = tid / LANES;  // local column of the first pass
+  const int lc = tid / LANES;  // this thread's column within the block
+  const int j = col_begin + lc;
   // dims beyond `dim` of the last lanes are read: zero the buffers once if there are any (the copies never touch them)
   if (dim < LANES * DPT)
     for (int idx = tid; idx < 2 * buf_floats; idx += blockDim.x) smem[idx] = 0.f;
   grid_dependency_wait();
   float* st = state + (size_t)seq_slot[s] * slot_stride + (size_t)head * vdim * dim;
 
-  float S[CPT][DPT];
+  float S[DPT];
+  if (vec_s) {
 #pragma unroll
-  for (int c = 0; c < CPT; c++) {
-    const int j = col_begin + lc0 + c * cols_per_pass;
-    if (vec_s) {
+    for (int i = 0; i < DPT; i += 4) {
+      const int d = 4 * (lane + LANES * (i >> 2));
+      const float4 x = (j < col_end && d < dim) ? *reinterpret_cast<const float4*>(st + (size_t)j * dim + d)
+                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+      S[i] = x.x; S[i + 1] = x.y; S[i + 2] = x.z; S[i + 3] = x.w;
+    }
+  } else {
 #pragma unroll
-      for (int i = 0; i < DPT; i += 4) {
-        const int d = lane * DPT + i;
-        const float4 x = (j < col_end && d < dim) ? *reinterpret_cast<const float4*>(st + (size_t)j * dim + d)
-                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
-        S[c][i] = x.x; S[c][i + 1] = x.y; S[c][i + 2] = x.z; S[c][i + 3] = x.w;
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < DPT; i++) {
-        const int d = lane * DPT + i;
-        S[c][i] = (j < col_end && d < dim) ? st[(size_t)j * dim + d] : 0.f;
-      }
+    for (int i = 0; i < DPT; i++) {
+      const int d = 4 * (lane + LANES * (i >> 2)) + (i & 3);
+      S[i] = (j < col_end && d < dim) ? st[(size_t)j * dim + d] : 0.f;
     }
   }
   const float* qh = q + (size_t)(head / qk_div) * dim;
@@ -183,37 +182,35 @@ decay_walk_kernel(const float* __restrict__ q, int q_stride, const float* __rest
 
   auto stage = [&](int t0, int b) {
     float* qs = smem + b * buf_floats;
-    float* ks = qs + CHUNK * QROW;
-    float* vs = ks + CHUNK * QROW;
-    float* as = vs + CHUNK * cols4;
-    float* cs = as + CHUNK;
-    const int nt = min(CHUNK, n - t0);
+    float* ks = qs + chunk * QROW;
+    float* vs = ks + chunk * QROW;
+    float* as = vs + chunk * cols4;
+    float* cs = as + chunk;
+    const int nt = min(chunk, n - t0);
     if (vec_qk) {
       const int d4n = dim >> 2;
       for (int idx = tid; idx < nt * d4n; idx += blockDim.x) {
-        const int t = idx / d4n, d = (idx - t * d4n) * 4;
-        const int at = t * QROW + (d / DPT) * (DPT + 4) + (d % DPT);
-        cp_async16(qs + at, qh + (size_t)(start + t0 + t) * q_stride + d);
-        cp_async16(ks + at, kh + (size_t)(start + t0 + t) * k_stride + d);
+        const int t = idx / d4n, d4 = idx - t * d4n;
+        cp_async16(qs + t * QROW + 4 * d4, qh + (size_t)(start + t0 + t) * q_stride + 4 * d4);
+        cp_async16(ks + t * QROW + 4 * d4, kh + (size_t)(start + t0 + t) * k_stride + 4 * d4);
       }
     } else {
       for (int idx = tid; idx < nt * dim; idx += blockDim.x) {
         const int t = idx / dim, d = idx - t * dim;
-        const int at = t * QROW + (d / DPT) * (DPT + 4) + (d % DPT);
-        cp_async4(qs + at, qh + (size_t)(start + t0 + t) * q_stride + d);
-        cp_async4(ks + at, kh + (size_t)(start + t0 + t) * k_stride + d);
+        cp_async4(qs + t * QROW + d, qh + (size_t)(start + t0 + t) * q_stride + d);
+        cp_async4(ks + t * QROW + d, kh + (size_t)(start + t0 + t) * k_stride + d);
       }
     }
     if (vec_v && (ncols & 3) == 0) {
       const int c4n = ncols >> 2;
       for (int idx = tid; idx < nt * c4n; idx += blockDim.x) {
-        const int t = idx / c4n, j = (idx - t * c4n) * 4;
-        cp_async16(vs + t * cols4 + j, vh + (size_t)(start + t0 + t) * v_stride + j);
+        const int t = idx / c4n, jj = (idx - t * c4n) * 4;
+        cp_async16(vs + t * cols4 + jj, vh + (size_t)(start + t0 + t) * v_stride + jj);
       }
     } else {
       for (int idx = tid; idx < nt * ncols; idx += blockDim.x) {
-        const int t = idx / ncols, j = idx - t * ncols;
-        cp_async4(vs + t * cols4 + j, vh + (size_t)(start + t0 + t) * v_stride + j);
+        const int t = idx / ncols, jj = idx - t * ncols;
+        cp_async4(vs + t * cols4 + jj, vh + (size_t)(start + t0 + t) * v_stride + jj);
       }
     }
     if (dt_dec != nullptr) {
@@ -227,87 +224,82 @@ decay_walk_kernel(const float* __restrict__ q, int q_stride, const float* __rest
 
   stage(0, 0);
   int b = 0;
-  for (int t0 = 0; t0 < n; t0 += CHUNK, b ^= 1) {
-    const int nt = min(CHUNK, n - t0);
-    if (t0 + CHUNK < n) {
-      stage(t0 + CHUNK, b ^ 1);
+  for (int t0 = 0; t0 < n; t0 += chunk, b ^= 1) {
+    const int nt = min(chunk, n - t0);
+    if (t0 + chunk < n) {
+      stage(t0 + chunk, b ^ 1);
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
     __syncthreads();
     const float* qs = smem + b * buf_floats;
-    const float* ks = qs + CHUNK * QROW;
-    const float* vs = ks + CHUNK * QROW;
-    const float* as = vs + CHUNK * cols4;
-    const float* cs = as + CHUNK;
-#pragma unroll 2
+    const float* ks = qs + chunk * QROW;
+    const float* vs = ks + chunk * QROW;
+    const float* as = vs + chunk * cols4;
+    const float* cs = as + chunk;
+    float* mine = os + (lc * LANES + lane) * orow;
+#pragma unroll 4
     for (int t = 0; t < nt; t++) {
       const float a = dt_dec ? as[t] : a_const, ck = dt_dec ? cs[t] : 1.f;
-      const float4* q4 = reinterpret_cast<const float4*>(qs + t * QROW + lane * (DPT + 4));
-      const float4* k4 = reinterpret_cast<const float4*>(ks + t * QROW + lane * (DPT + 4));
+      const float4* q4 = reinterpret_cast<const float4*>(qs + t * QROW) + lane;
+      const float4* k4 = reinterpret_cast<const float4*>(ks + t * QROW) + lane;
+      const float vj = lc < ncols ? vs[t * cols4 + lc] : 0.f;
+      const float cv = ck * vj;
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-      for (int c = 0; c < CPT; c++) {
-        const int lc = lc0 + c * cols_per_pass;
-        const float vj = lc < ncols ? vs[t * cols4 + lc] : 0.f;
-        const float cv = ck * vj;
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll
-        for (int i = 0; i < DPT / 4; i++) {
-          const float4 qq = q4[i], kk = k4[i];
-          S[c][4 * i + 0] = fmaf(a, S[c][4 * i + 0], kk.x * cv);
-          S[c][4 * i + 1] = fmaf(a, S[c][4 * i + 1], kk.y * cv);
-          S[c][4 * i + 2] = fmaf(a, S[c][4 * i + 2], kk.z * cv);
-          S[c][4 * i + 3] = fmaf(a, S[c][4 * i + 3], kk.w * cv);
-          a0 = fmaf(S[c][4 * i + 0], qq.x, a0);
-          a1 = fmaf(S[c][4 * i + 1], qq.y, a1);
-          a2 = fmaf(S[c][4 * i + 2], qq.z, a2);
-          a3 = fmaf(S[c][4 * i + 3], qq.w, a3);
-        }
-        float acc = (a0 + a1) + (a2 + a3);
-        if (defer) {
-          // few columns a block (one or two warps): a warp that waited for three shuffles a token would have nothing
-          // else to issue; the lanes' shares go to shared memory and are added up after the chunk
-          if (lc < ncols) os[(t * cols + lc) * LANES + lane] = lane == 0 ? fmaf(d_skip, vj, acc) : acc;
-        } else {
-          acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-          acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-          acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-          if (lane == 0 && lc < ncols) os[t * cols + lc] = fmaf(d_skip, vj, acc);
-        }
+      for (int i = 0; i < DPT / 4; i++) {
+        const float4 qq = q4[LANES * i], kk = k4[LANES * i];
+        S[4 * i + 0] = fmaf(a, S[4 * i + 0], kk.x * cv);
+        S[4 * i + 1] = fmaf(a, S[4 * i + 1], kk.y * cv);
+        S[4 * i + 2] = fmaf(a, S[4 * i + 2], kk.z * cv);
+        S[4 * i + 3] = fmaf(a, S[4 * i + 3], kk.w * cv);
+        a0 = fmaf(S[4 * i + 0], qq.x, a0);
+        a1 = fmaf(S[4 * i + 1], qq.y, a1);
+        a2 = fmaf(S[4 * i + 2], qq.z, a2);
+        a3 = fmaf(S[4 * i + 3], qq.w, a3);
       }
+      // this lane's share of o_t goes to shared memory; the shares are added up after the chunk (a shuffle sum here
+      // would make every token wait for five dependent shuffles)
+      const float acc = (a0 + a1) + (a2 + a3);
+      mine[t] = lane == 0 ? fmaf(d_skip, vj, acc) : acc;
     }
-    __syncthreads();  // the chunk's outputs are complete; its buffer may be filled again (by the stage after next)
-    for (int idx = tid; idx < nt * ncols; idx += blockDim.x) {
-      const int t = idx / ncols, j = idx - t * ncols;
-      float o;
-      if (defer) {
-        const float4 x = *reinterpret_cast<const float4*>(os + (t * cols + j) * LANES);
-        const float4 y = *reinterpret_cast<const float4*>(os + (t * cols + j) * LANES + 4);
-        o = ((x.x + x.y) + (x.z + x.w)) + ((y.x + y.y) + (y.z + y.w));
+    __syncwarp();  // a column's lanes are one warp, or part of one: its shares are all there
+    // add the shares up: the lanes of a column split the chunk's tokens among them
+    if (lc < ncols) {
+      float* col_out = out + (size_t)(start + t0) * heads * vdim + (size_t)head * vdim + j;
+      const float* shares = os + (size_t)lc * LANES * orow;
+      if (LANES == 32 && chunk == 16) {
+        const int t = lane & 15, l0 = (lane >> 4) * 16;
+        float sum = 0.f;
+#pragma unroll
+        for (int l = 0; l < 16; l++) sum += shares[(l0 + l) * orow + t];
+        sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+        if (lane < 16 && t < nt) col_out[(size_t)t * heads * vdim] = sum;
       } else {
-        o = os[t * cols + j];
+        for (int t = lane; t < nt; t += LANES) {
+          float sum = 0.f;
+#pragma unroll
+          for (int l = 0; l < LANES; l++) sum += shares[l * orow + t];
+          col_out[(size_t)t * heads * vdim] = sum;
+        }
       }
-      out[(size_t)(start + t0 + t) * heads * vdim + (size_t)head * vdim + col_begin + j] = o;
     }
+    __syncthreads();  // the chunk's buffer may be filled again (by the stage after next), the shares overwritten
   }
   if (write_state) {
+    if (vec_s) {
 #pragma unroll
-    for (int c = 0; c < CPT; c++) {
-      const int j = col_begin + lc0 + c * cols_per_pass;
-      if (vec_s) {
+      for (int i = 0; i < DPT; i += 4) {
+        const int d = 4 * (lane + LANES * (i >> 2));
+        if (j < col_end && d < dim)
+          *reinterpret_cast<float4*>(st + (size_t)j * dim + d) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+      }
+    } else {
 #pragma unroll
-        for (int i = 0; i < DPT; i += 4) {
-          const int d = lane * DPT + i;
-          if (j < col_end && d < dim)
-            *reinterpret_cast<float4*>(st + (size_t)j * dim + d) = make_float4(S[c][i], S[c][i + 1], S[c][i + 2], S[c][i + 3]);
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < DPT; i++) {
-          const int d = lane * DPT + i;
-          if (j < col_end && d < dim) st[(size_t)j * dim + d] = S[c][i];
-        }
+      for (int i = 0; i < DPT; i++) {
+        const int d = 4 * (lane + LANES * (i >> 2)) + (i & 3);
+        if (j < col_end && d < dim) st[(size_t)j * dim + d] = S[i];
       }
     }
   }
@@ -318,25 +310,19 @@ int walk_launch(const float* q, int q_stride, const float* k, int k_stride, int 
                 float* out, const int* seq_slot, const int* seq_q_start, const int* seq_q_len, int n_seqs, int n_tokens,
                 int heads, int dim, int vdim, int write_state, cudaStream_t st) {
   if (n_seqs <= 0 || n_tokens <= 0) return 0;
-  if (dim <= 0 || dim > DPT * LANES || vdim <= 0 || vdim > CPT * 128 || heads <= 0 || qk_div <= 0) return -2;
+  if (dim <= 0 || dim > DPT * LANES || vdim <= 0 || heads <= 0 || qk_div <= 0) return -2;
   if (heads > 65535) return -3;
-  int cols_per_block = vdim;
-  if (n_tokens > n_seqs) {  // portions: spread a head's columns over blocks until the SMs are filled four times
-    const int want = 4 * sm_count();
-    const int have = n_seqs * heads;
-    const int splits = have >= want ? 1 : (want + have - 1) / have;
-    cols_per_block = (vdim + splits - 1) / splits;
-    cols_per_block = ((cols_per_block + 3) / 4) * 4;
-    if (cols_per_block > vdim) cols_per_block = vdim;
-  }
+  // blocks of 256 threads: every block stages the head's q and k for itself (thinner blocks would pay more for that),
+  // and several fit an SM with their loads of the state in flight together.  A step in which no request brings more
+  // than one token stages one token at a time.
+  const int chunk = n_tokens > n_seqs ? CHUNK : 1;
+  int cols_per_block = 256 / LANES;
+  if (cols_per_block > vdim) cols_per_block = vdim;
   const int splits = (vdim + cols_per_block - 1) / cols_per_block;
-  int per_pass = (cols_per_block + CPT - 1) / CPT;
-  if (per_pass > 128) per_pass = 128;
-  int threads = ((per_pass * LANES + 31) / 32) * 32;
-  const int cols = cols_per_block < vdim ? cols_per_block : vdim;
-  const int cols4 = (cols + 3) & ~3;
-  const int defer = cols <= 16;
-  const size_t smem = (size_t)(2 * CHUNK * (2 * QROW + cols4 + 2) + CHUNK * cols * (defer ? LANES : 1)) * sizeof(float);
+  if (splits > 65535) return -3;
+  const int threads = ((cols_per_block * LANES + 31) / 32) * 32;
+  const int cols4 = (cols_per_block + 3) & ~3;
+  const size_t smem = (size_t)(2 * chunk * (2 * QROW + cols4 + 2) + cols_per_block * LANES * (chunk + 1)) * sizeof(float);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(decay_walk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -347,7 +333,7 @@ int walk_launch(const float* q, int q_stride, const float* k, int k_stride, int 
   const int vec_s = dim % 4 == 0 && slot_stride % 4 == 0 && al16(state);
   return launch_pdl(decay_walk_kernel, dim3(n_seqs, heads, splits), dim3(threads), smem, st, q, q_stride, k, k_stride,
                     qk_div, v, v_stride, dt_dec, decay_head, skip, state, slot_stride, out, seq_slot, seq_q_start,
-                    seq_q_len, heads, dim, vdim, write_state, cols_per_block, vec_qk, vec_v, vec_s, defer);
+                    seq_q_len, heads, dim, vdim, write_state, cols_per_block, vec_qk, vec_v, vec_s, chunk);
 }
 
 }  // namespace

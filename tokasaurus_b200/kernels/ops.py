@@ -1061,9 +1061,16 @@ def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, 
 
 # ---------------------------------------------------------------------------------------------
 # The recurrence with one decay a head and token (csrc/decay_recurrence.cu)
-def decay_recurrence_defines(dim: int, vdim: int) -> dict:
-    _need(0 < dim <= 256 and 0 < vdim <= 512, f"decay recurrence: heads up to 256 x 512, not {dim} x {vdim}")
-    return dict(TKB_DR_DPT=4 * ((dim + 31) // 32), TKB_DR_CPT=(vdim + 127) // 128)
+def decay_recurrence_defines(dim: int, vdim: int, single: bool = False) -> dict:
+    """The compile-time constants of the walk for heads of ``dim`` x ``vdim``: how many threads share a column of the
+    state and how many values each holds.  Portions: 8, 16 or 32 threads, as many as the head has 16-byte pieces (the
+    walk over the tokens is a chain, so it is spread over as many warps as the state allows).  ``single`` (steps in which
+    every request brings one token): 8 threads with more values each, so that a thread has several 16-byte loads of the
+    state in flight (the time is the state's trip through memory)."""
+    _need(0 < dim <= 1024 and 0 < vdim, f"decay recurrence: key sizes up to 1024, not {dim}")
+    pieces = (dim + 3) // 4
+    lanes = 8 if (single or pieces <= 8) else (16 if pieces <= 16 else 32)
+    return dict(TKB_DR_LANES=lanes, TKB_DR_DPT=4 * ((pieces + lanes - 1) // lanes))
 
 
 def ssm_prep(proj: torch.Tensor, xbc_off: int, channels: int, conv_w: torch.Tensor, conv_b: torch.Tensor | None,
@@ -1117,6 +1124,8 @@ def decay_walk(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads_per_qk: 
     _need(state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous() and state.shape[1] >= heads * vdim * dim,
           "decay_walk: state float32 [slots, n]")
     _need(out.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape) == (T, heads * vdim), "decay_walk: out float32 [T, heads * vdim]")
+    if T == n_seqs:  # no request brings more than one token
+        defines = decay_recurrence_defines(dim, vdim, single=True)
     _check(_fn(_libs.get("decay_recurrence.cu", **defines), "tkb_decay_walk")(
         _ptr(q), c_int(q.stride(0)), _ptr(k), c_int(k.stride(0)), c_int(heads_per_qk), _ptr(v), c_int(v.stride(0)),
         _ptr(dt_dec), _ptr(decay_head), _ptr(skip), _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(out),

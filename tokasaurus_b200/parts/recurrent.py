@@ -85,6 +85,7 @@ class DecayedLinearAttention(Mixer):
         self.norm_eps = float(norm_eps)
         self.names = dict(q=q_name, k=k_name, v=v_name, g=g_name, norm=norm_name, o=o_name)
         self.defines = ops.decay_recurrence_defines(dim, vdim)  # refuses sizes the kernel does not take
+        self.defines_single = ops.decay_recurrence_defines(dim, vdim, single=True)
 
     def weight_specs(self):
         n, H, d, e = self.names, self.n_heads, self.dim, self.vdim
@@ -93,7 +94,7 @@ class DecayedLinearAttention(Mixer):
                 WeightSpec(n["o"], (self.width, H * e)), WeightSpec(n["norm"], (H * e,), role="vector"))
 
     def kernel_modules(self, dtype):
-        return (("decay_recurrence.cu", self.defines), ("post_norm.cu", None))
+        return (("decay_recurrence.cu", self.defines), ("decay_recurrence.cu", self.defines_single), ("post_norm.cu", None))
 
     def cache_need(self):
         return StateNeed((self.n_heads * self.vdim * self.dim,), "float32")  # S^T: [head][value][key channel]

@@ -41,6 +41,7 @@ class SelectiveStateSpace(Mixer):
         self.names = dict(w_in=in_name, conv=conv_name, conv_b=conv_bias_name, dt_bias=dt_bias_name, a_log=a_log_name,
                           d=d_name, norm=norm_name, o=o_name)
         self.defines = ops.decay_recurrence_defines(state, vdim)
+        self.defines_single = ops.decay_recurrence_defines(state, vdim, single=True)
 
     def weight_specs(self):
         n, H = self.names, self.n_heads
@@ -52,7 +53,7 @@ class SelectiveStateSpace(Mixer):
                 WeightSpec(n["o"], (self.width, self.inner)))
 
     def kernel_modules(self, dtype):
-        return (("decay_recurrence.cu", self.defines), ("post_norm.cu", None))
+        return (("decay_recurrence.cu", self.defines), ("decay_recurrence.cu", self.defines_single), ("post_norm.cu", None))
 
     def cache_need(self):
         # [S^T of every head: heads x vdim x state | the convolution's last taps - 1 inputs: (taps - 1) x channels]
