@@ -285,18 +285,21 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// cap * tanh(s / cap) in units of log2: tanh(x) = 1 - 2 / (e^(2x) + 1), the exponential of a bounded argument
+// cap * tanh(s / cap) in units of log2: tanh(x) = 1 - 2 / (e^(2x) + 1) with the exponential of a bounded argument.
+// The exponential and the quotient are each good to about 1e-7 of a result near 1, so the capped score is off by about
+// cap * 1e-7: the size of a float32 rounding of a score of the cap's own size (the FP32-pipe kernel calls tanhf).
 __device__ __forceinline__ float capped_log2(float s, float softcap, float inv_cap) {
   if (softcap > 0.f) {
     const float x = fminf(fmaxf(s * inv_cap, -15.f), 15.f);
     const float e = ex2(2.f * LOG2E * x);
-    // near zero 1 - 2 / (e + 1) loses digits: there tanh(x) = x - x^3 / 3 + 2 x^5 / 15 is exact to float32
-    const float x2 = x * x;
-    const float t = fabsf(x) < 0.125f ? x * (1.f - x2 * (0.33333334f - x2 * (0.13333334f - x2 * 0.053968254f)))
-                                       : 1.f - __fdividef(2.f, e + 1.f);
-    s = softcap * t;
+    s = fmaf(-softcap, __fdividef(2.f, e + 1.f), softcap);
   }
   return s * LOG2E;
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 
 // Keys k0 .. k0 + 63 of the request into one buffer: a cached row [k | v] is one run of 16-byte pieces.  Rows outside
@@ -327,12 +330,24 @@ __device__ __forceinline__ void attend(const bf16* buf, int kr0, int key0, const
 #pragma unroll
   for (int nt = 0; nt < NT; nt++) {
     sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
-    const bf16* krow = buf + (kr0 + nt * 8 + g) * RS + 2 * t;
+    if constexpr (KSTEPS % 2 == 0) {
+      // four 8 x 8 pieces a load: keys nt * 8 .. + 7, key channels of two k-steps (a piece's row is one key's 8 channels)
+      const bf16* kp = buf + (kr0 + nt * 8 + (lane & 7)) * RS + (lane >> 3) * 8;
 #pragma unroll
-    for (int ks = 0; ks < KSTEPS; ks++) {
-      const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks * 16);
-      const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ks * 16 + 8);
-      mma_bf16(sc[nt], qf[ks], b0, b1);
+      for (int ks = 0; ks < KSTEPS; ks += 2) {
+        uint32_t b[4];
+        ldmatrix_x4(b, smem_u32(kp + ks * 16));
+        mma_bf16(sc[nt], qf[ks], b[0], b[1]);
+        mma_bf16(sc[nt], qf[ks + 1], b[2], b[3]);
+      }
+    } else {
+      const bf16* krow = buf + (kr0 + nt * 8 + g) * RS + 2 * t;
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ks++) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks * 16);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ks * 16 + 8);
+        mma_bf16(sc[nt], qf[ks], b0, b1);
+      }
     }
   }
   float alpha[2];
