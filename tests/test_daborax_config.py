@@ -49,6 +49,9 @@ def test_description_follows_the_configuration():
     mods = {(src, tuple(sorted((dd or {}).items()))) for src, dd in model.kernel_modules("bfloat16")}
     assert ("attention_sink.cu", (("TKB_QK", 24), ("TKB_VD", 40))) in mods
     assert ("decay_recurrence.cu", (("TKB_DR_DPT", 4), ("TKB_DR_LANES", 8))) in mods   # state 20, dim 16: five and four 16-byte pieces
+    from tokasaurus_b200.kernels import ops
+    assert [d["TKB_DR_LANES"] for d in ops.decay_walk_modules(128, 64)] == [8, 16, 32]
+    assert ops.decay_walk_modules(40, 8) == [dict(TKB_DR_LANES=8, TKB_DR_DPT=8), dict(TKB_DR_LANES=16, TKB_DR_DPT=4)]
     att, ssm, lin = (b.mixer for b in model.blocks)
     assert (att.scale, att.softcap, att.window) == (0.4, 8.0, 23) and lin.decay == (0.7, 0.95, 0.999)
     assert model.blocks[0].mult == 0.6 and model.embedding.scale == 3.5 and model.blocks[2].ffn.limit == 0.8

@@ -162,8 +162,14 @@ def test_convolution_step_sizes_and_carried_inputs(ops, taps):
 @pytest.mark.parametrize("heads,groups,dim,vdim", [(4, 2, 24, 40), (2, 2, 64, 16), (1, 1, 7, 130), (6, 1, 128, 64), (3, 3, 10, 300), (2, 1, 200, 36)])
 def test_decay_walk_in_portions(ops, heads, groups, dim, vdim):
     """Both forms (a decay per head, silu on the inputs; decays and key scales per token with a skip term and shared
-    q and k per group) over two requests in portions down to one token, against the whole sequences."""
+    q and k per group) over two requests in portions down to one token, against the whole sequences, with every build
+    of the walk that the head size allows (8, 16, 32 threads a column)."""
     defines = walk_defines(ops, dim, vdim)
+    builds = ops.decay_walk_modules(dim, vdim)
+    import itertools
+    chosen = itertools.cycle(builds)  # a request's steps go through different builds: the state's layout is one
+    monkey = pytest.MonkeyPatch()
+    monkey.setattr(ops, "_walk_defines", lambda *a: next(chosen))
     g = torch.Generator().manual_seed(heads * 1000 + dim)
     lens = {0: 70, 1: 19}
     portions = {0: [2, 33, 1, 1, 17, 16], 1: [1, 2, 16]}
@@ -196,11 +202,10 @@ def test_decay_walk_in_portions(ops, heads, groups, dim, vdim):
                 ops.silu_cols(wide, wide.shape[1] - 3, defines)
                 assert float((wide[:, -3:] - 9.0).abs().max()) == 0.0
                 ops.decay_walk(wide[:, :G * dim], wide[:, G * dim:2 * G * dim], wide[:, 2 * G * dim:-3], 1, None, decay.to(DEV),
-                               None, state, out, i32([slots[s] for s in live]), i32(qs), i32(ql), len(live), heads, dim, vdim,
-                               defines)
+                               None, state, out, i32([slots[s] for s in live]), i32(qs), i32(ql), len(live), heads, dim, vdim)
             else:
                 ops.decay_walk(cat(q), cat(k), cat(v), heads // groups, cat(dd), None, skip.to(DEV), state, out,
-                               i32([slots[s] for s in live]), i32(qs), i32(ql), len(live), heads, dim, vdim, defines)
+                               i32([slots[s] for s in live]), i32(qs), i32(ql), len(live), heads, dim, vdim)
             for s, a, n in zip(live, qs, ql):
                 got[s].append(out[a:a + n].cpu())
                 at[s] += n
@@ -229,6 +234,7 @@ def test_decay_walk_in_portions(ops, heads, groups, dim, vdim):
                 left = state[slots[s], :n_state].cpu().reshape(heads, vdim, dim)
                 assert rel_err(left, S.transpose(1, 2)) < 2e-5
         assert float((state[:, n_state:] - 5.0).abs().max()) == 0.0
+    monkey.undo()
 
 
 def paged(n_tokens, page, seed):
@@ -312,6 +318,41 @@ def test_sink_attention_window_edges(ops, dtype, dim, vdim, page, heads, kv):
     ops.attn_sink(qd, out, cache, i32([0] * 40), i32(pos), i32([0, need]), i32(table), i32(rows), 3, None, heads, kv, dim,
                   vdim, page, scale / dim ** 0.5, None, None, status)
     assert rel_err(out.float().cpu(), want.reshape(40, -1)[rows]) < (3e-5 if dtype == "float32" else 3e-2)
+
+
+@pytest.mark.parametrize("window", [None, 130])
+def test_sink_attention_single_tokens_over_several_blocks(ops, window):
+    """Three requests that bring one token each at contexts of 300, 70 and 1: with so few requests a request's keys are
+    shared out among several blocks (one of them gets the sink, some get no keys at all) and put together afterwards."""
+    dim, vdim, heads, kv, page = 32, 48, 6, 2, 16
+    g = torch.Generator().manual_seed(9)
+    sinks = torch.randn(heads, generator=g) + 1
+    lens = [300, 70, 1]
+    qkv_w = (heads + kv) * dim + kv * vdim
+    n_pages = sum(-(-n // page) for n in lens)
+    cache = torch.full((n_pages, kv, page, dim + vdim), float("nan"), dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    perm = [int(x) for x in np.random.default_rng(3).permutation(n_pages)]
+    tables, want, last_q = [], [], []
+    for n in lens:
+        raw = torch.randn(n, qkv_w, generator=g)
+        table, perm = perm[:-(-n // page)], perm[-(-n // page):]
+        tables.append(table)
+        qd = torch.empty(n, heads * dim, dtype=torch.bfloat16, device=DEV)
+        ops.sink_attn_prep(raw.to(DEV), None, True, 1e-6, qd, cache, i32(list(range(n))), i32([0] * n), i32([0, len(table)]),
+                           i32(table), heads, kv, dim, vdim, page, True, status)
+        last_q.append(qd[-1:])
+        x = raw.double()
+        q = plain.rms_norm(x[:, :heads * dim].reshape(n, heads, dim), None, 1e-6)
+        k = plain.rms_norm(x[:, heads * dim:(heads + kv) * dim].reshape(n, kv, dim), None, 1e-6)
+        v = x[:, (heads + kv) * dim:].reshape(n, kv, vdim)
+        want.append(plain.window_sink_attention(q, k, v, sinks.double(), 0.35, 20.0, window).reshape(n, -1)[-1])
+    indptr = [0] + [int(x) for x in np.cumsum([len(t) for t in tables])]
+    out = torch.full((3, heads * vdim), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.attn_sink_tc(torch.cat(last_q), out, cache, i32([0, 1, 2]), i32([1, 1, 1]), i32(lens), i32(indptr),
+                     i32(sum(tables, [])), 3, sinks.to(DEV), heads, kv, dim, vdim, page, 0.35, 20.0, window, status, portions=False)
+    assert int(status.item()) == 0
+    assert rel_err(out.float().cpu(), torch.stack(want)) < 3e-2
 
 
 # ------------------------------------------------------------------------------------------------ whole models

@@ -21,7 +21,8 @@
 // value arrive in one copy) and keep a running softmax that the sink opens.  attn_sink_tiles: a block owns 64 queries
 // of one request's portion and one query head, a warp 16 of them.  attn_sink_single: a block owns a request that
 // brings one token and one key/value head; the MMA rows are that head's query heads, the four warps take every
-// fourth group of 16 keys and are merged through shared memory.  Blocks find their work from the step's request
+// fourth group of 16 keys and are merged through shared memory; with few requests a request's tiles are shared out
+// among several blocks and a small kernel puts their shares together.  Blocks find their work from the step's request
 // table themselves, so a launch depends on the step's shape only.
 //
 // Compile with -DTKB_QK=<query/key size> -DTKB_VD=<value size>.
@@ -505,12 +506,14 @@ attn_sink_single_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
                         const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
                         const int* __restrict__ seq_kv_len, const int* __restrict__ page_indptr,
                         const int* __restrict__ page_ids, const float* __restrict__ sinks, int nh, int nkv, int head_tiles,
-                        int ps, float scale, float softcap, int window, int num_pages, int* __restrict__ status) {
+                        int ps, float scale, float softcap, int window, int num_pages, int* __restrict__ status,
+                        float* __restrict__ part) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* bufs = reinterpret_cast<bf16*>(smem_raw);
   trigger_dependents();
   const int s = blockIdx.x;
   if (seq_q_len[s] != 1) return;
+  const int splits = gridDim.z, split = blockIdx.z;
   grid_dependency_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int group = nh / nkv;
@@ -537,30 +540,36 @@ attn_sink_single_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
       qf[ks][hh + 2] = live ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t) : 0u;
     }
     m[hh] = sinks ? sinks[head] * LOG2E : NEG_BIG;
-    l[hh] = (sinks && warp == 0 && t == 0) ? 1.f : 0.f;  // the sink counts once: in the first warp's sums
+    l[hh] = (sinks && split == 0 && warp == 0 && t == 0) ? 1.f : 0.f;  // the sink counts once: in one warp's sums
   }
   float o[VT][4];
 #pragma unroll
   for (int vt = 0; vt < VT; vt++) o[vt][0] = o[vt][1] = o[vt][2] = o[vt][3] = 0.f;
 
-  const int n_tiles = (p - k_lo) / KT + 1;
+  // the request's tiles are shared out evenly among the splits (blockIdx.z); a split may be left without any
+  const int all_tiles = (p - k_lo) / KT + 1;
+  const int per_split = (all_tiles + splits - 1) / splits;
+  const int it0 = split * per_split;
+  const int n_tiles = min(all_tiles, it0 + per_split) - it0;
   bool bad = false;
-  stage_tile(bufs, cache, table, k_lo, k_lo, p, kvh, nkv, ps, num_pages, bad, tid);
+  if (n_tiles > 0) stage_tile(bufs, cache, table, k_lo + it0 * KT, k_lo, p, kvh, nkv, ps, num_pages, bad, tid);
   cp_async_commit();
   for (int it = 0; it < n_tiles; it++) {
     bf16* cur = bufs + (it & 1) * KT * RS;
     if (it + 1 < n_tiles) {
-      stage_tile(bufs + ((it + 1) & 1) * KT * RS, cache, table, k_lo + (it + 1) * KT, k_lo, p, kvh, nkv, ps, num_pages, bad, tid);
+      stage_tile(bufs + ((it + 1) & 1) * KT * RS, cache, table, k_lo + (it0 + it + 1) * KT, k_lo, p, kvh, nkv, ps, num_pages, bad,
+                 tid);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
     __syncthreads();
-    const int key0 = k_lo + it * KT + warp * 16;
+    const int key0 = k_lo + (it0 + it) * KT + warp * 16;
     if (key0 <= p) attend<2>(cur, warp * 16, key0, qf, o, m, l, lim_lo, lim_hi, scale, softcap, inv_cap, lane);
     __syncthreads();
   }
+  cp_async_wait<0>();
   report_bad_page(bad, status);
 #pragma unroll
   for (int hh = 0; hh < 2; hh++) {
@@ -597,7 +606,38 @@ attn_sink_single_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
       acc += f * so[(w * 16 + r) * SO + d];
       ll += f * sml[(w * 16 + r) * 2 + 1];
     }
-    out[((size_t)tok * nh + kvh * group + g0 + r) * VD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+    const int head = kvh * group + g0 + r;
+    if (splits == 1) {
+      out[((size_t)tok * nh + head) * VD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+    } else {  // this split's share: sums relative to its own maximum, for attn_sink_merge
+      float* pr = part + (((size_t)s * nh + head) * splits + split) * (VD + 2);
+      pr[d] = acc;
+      if (d == 0) {
+        pr[VD] = mm;
+        pr[VD + 1] = ll;
+      }
+    }
+  }
+}
+
+// The splits of every single-token request put together: grid (request row, query head).
+__global__ void attn_sink_merge_kernel(const float* __restrict__ part, bf16* __restrict__ out,
+                                       const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len, int nh,
+                                       int splits) {
+  trigger_dependents();
+  grid_dependency_wait();
+  const int s = blockIdx.x, head = blockIdx.y;
+  if (seq_q_len[s] != 1) return;
+  const float* pr = part + ((size_t)s * nh + head) * splits * (VD + 2);
+  float mm = NEG_BIG;
+  for (int z = 0; z < splits; z++) mm = fmaxf(mm, pr[z * (VD + 2) + VD]);
+  float ll = 0.f;
+  for (int z = 0; z < splits; z++) ll += exp2f(pr[z * (VD + 2) + VD] - mm) * pr[z * (VD + 2) + VD + 1];
+  const float inv = ll > 0.f ? 1.f / ll : 0.f;
+  for (int d = threadIdx.x; d < VD; d += blockDim.x) {
+    float acc = 0.f;
+    for (int z = 0; z < splits; z++) acc += exp2f(pr[z * (VD + 2) + VD] - mm) * pr[z * (VD + 2) + d];
+    out[((size_t)seq_q_start[s] * nh + head) * VD + d] = __float2bfloat16_rn(acc * inv);
   }
 }
 
@@ -605,11 +645,13 @@ attn_sink_single_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
 
 // Attention of every token of the step (bfloat16): requests with one token through attn_sink_single, longer portions
 // through attn_sink_tiles.  n_tokens and n_seqs size the grids; the blocks read the rest from the request table.
+// splits > 1: a single-token request's tiles are shared out among so many blocks, whose shares meet in `part`
+// (float32 [n_seqs * nh * splits * (VD + 2)]) and are put together by attn_sink_merge.
 TKB_EXPORT int tkb_attn_sink_tc_bf16(const void* q, void* out, const void* cache, const int* seq_q_start,
                                      const int* seq_q_len, const int* seq_kv_len, const int* page_indptr,
                                      const int* page_ids, int n_tokens, int n_seqs, int portions, int singles,
                                      const float* sinks, int nh, int nkv, int page_size, float scale, float softcap,
-                                     int window, int num_pages, int* status, void* st) {
+                                     int window, int num_pages, int* status, float* part, int splits, void* st) {
   if (n_tokens <= 0 || n_seqs <= 0) return 0;
   if (nkv <= 0 || nh % nkv != 0 || page_size <= 0) return -2;
   const int head_tiles = (nh / nkv + 15) / 16;
@@ -621,10 +663,16 @@ TKB_EXPORT int tkb_attn_sink_tc_bf16(const void* q, void* out, const void* cache
     if (e != cudaSuccess) return (int)e;
   }
   int rc = 0;
-  if (singles)
-    rc = launch_pdl(attn_sink_single_kernel, dim3(n_seqs, nkv * head_tiles), dim3(128), TC_SMEM, (cudaStream_t)st,
+  if (splits < 1 || part == nullptr) splits = 1;
+  if (splits > 64) return -2;
+  if (singles) {
+    rc = launch_pdl(attn_sink_single_kernel, dim3(n_seqs, nkv * head_tiles, splits), dim3(128), TC_SMEM, (cudaStream_t)st,
                     (const bf16*)q, (bf16*)out, (const bf16*)cache, seq_q_start, seq_q_len, seq_kv_len, page_indptr,
-                    page_ids, sinks, nh, nkv, head_tiles, page_size, scale, softcap, window, num_pages, status);
+                    page_ids, sinks, nh, nkv, head_tiles, page_size, scale, softcap, window, num_pages, status, part);
+    if (rc == 0 && splits > 1)
+      rc = launch_pdl(attn_sink_merge_kernel, dim3(n_seqs, nh), dim3(VD >= 128 ? 128 : 64), 0, (cudaStream_t)st,
+                      (const float*)part, (bf16*)out, seq_q_start, seq_q_len, nh, splits);
+  }
   if (rc != 0 || !portions) return rc;
   const int tiles = n_tokens / KT + n_seqs;  // no step of this shape has more 64-query tiles
   return launch_pdl(attn_sink_tiles_kernel, dim3(tiles, nh), dim3(128), TC_SMEM, (cudaStream_t)st, (const bf16*)q,

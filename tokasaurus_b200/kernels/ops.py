@@ -1061,16 +1061,44 @@ def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, 
 
 # ---------------------------------------------------------------------------------------------
 # The recurrence with one decay a head and token (csrc/decay_recurrence.cu)
-def decay_recurrence_defines(dim: int, vdim: int, single: bool = False) -> dict:
+def decay_recurrence_defines(dim: int, vdim: int, lanes: int | None = None) -> dict:
     """The compile-time constants of the walk for heads of ``dim`` x ``vdim``: how many threads share a column of the
-    state and how many values each holds.  Portions: 8, 16 or 32 threads, as many as the head has 16-byte pieces (the
-    walk over the tokens is a chain, so it is spread over as many warps as the state allows).  ``single`` (steps in which
-    every request brings one token): 8 threads with more values each, so that a thread has several 16-byte loads of the
-    state in flight (the time is the state's trip through memory)."""
+    state (``lanes``: 8, 16 or 32, at most as many as the head has 16-byte pieces; None: 8) and how many values each
+    holds."""
     _need(0 < dim <= 1024 and 0 < vdim, f"decay recurrence: key sizes up to 1024, not {dim}")
     pieces = (dim + 3) // 4
-    lanes = 8 if (single or pieces <= 8) else (16 if pieces <= 16 else 32)
+    lanes = min(lanes or 8, 8 if pieces <= 8 else (16 if pieces <= 16 else 32))
+    _need(lanes in (8, 16, 32), "decay recurrence: 8, 16 or 32 threads a column")
     return dict(TKB_DR_LANES=lanes, TKB_DR_DPT=4 * ((pieces + lanes - 1) // lanes))
+
+
+def decay_walk_modules(dim: int, vdim: int) -> list[dict]:
+    """Every build of the walk that ``decay_walk`` may choose for heads of this size."""
+    out = []
+    for lanes in (8, 16, 32):
+        d = decay_recurrence_defines(dim, vdim, lanes)
+        if d not in out:
+            out.append(d)
+    return out
+
+
+def _walk_defines(dim: int, vdim: int, columns: int, single: bool, device) -> dict:
+    """Which build walks ``columns`` state columns (requests x heads x vdim).  Single tokens: 8 threads a column, each
+    with several 16-byte loads of the state in flight (the time is the state's trip through memory).  Portions: the
+    walk over the tokens is a chain, a warp alone issues an instruction every four cycles, so the columns are spread
+    over warps until there are about seven an SM (measured on B200 at heads of 128 x 128 and 64 x 128, 2,048 tokens:
+    1,024 warps beat 512 and 2,048 at 16, 32 and 64 heads alike), by giving a column more threads with fewer values."""
+    if single:
+        return decay_recurrence_defines(dim, vdim, 8)
+    from tokasaurus_b200.kernels.device import device_limits
+
+    want = 6 * device_limits(device).sm_count
+    chosen = None
+    for d in decay_walk_modules(dim, vdim):
+        chosen = d
+        if columns * d["TKB_DR_LANES"] // 32 >= want:
+            break
+    return chosen
 
 
 def ssm_prep(proj: torch.Tensor, xbc_off: int, channels: int, conv_w: torch.Tensor, conv_b: torch.Tensor | None,
@@ -1105,7 +1133,7 @@ def ssm_prep(proj: torch.Tensor, xbc_off: int, channels: int, conv_w: torch.Tens
 def decay_walk(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads_per_qk: int, dt_dec: torch.Tensor | None,
                decay_head: torch.Tensor | None, skip: torch.Tensor | None, state: torch.Tensor, out: torch.Tensor,
                seq_slot: torch.Tensor, seq_q_start: torch.Tensor, seq_q_len: torch.Tensor, n_seqs: int, heads: int,
-               dim: int, vdim: int, defines: dict, write_state: bool = True) -> None:
+               dim: int, vdim: int, write_state: bool = True) -> None:
     """S_t = a_t S_(t-1) + (c_t k_t) v_t^T, o_t = S_t^T q_t + skip * v_t over each request's tokens.  q, k [T, . * dim]
     and v [T, heads * vdim] are float32 (column slices allowed); head h reads q and k number h // heads_per_qk.
     ``dt_dec`` [T, 2 heads] = (c, a) per token, or ``decay_head`` [heads] with
@@ -1124,8 +1152,7 @@ def decay_walk(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads_per_qk: 
     _need(state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous() and state.shape[1] >= heads * vdim * dim,
           "decay_walk: state float32 [slots, n]")
     _need(out.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape) == (T, heads * vdim), "decay_walk: out float32 [T, heads * vdim]")
-    if T == n_seqs:  # no request brings more than one token
-        defines = decay_recurrence_defines(dim, vdim, single=True)
+    defines = _walk_defines(dim, vdim, n_seqs * heads * vdim, T == n_seqs, q.device)
     _check(_fn(_libs.get("decay_recurrence.cu", **defines), "tkb_decay_walk")(
         _ptr(q), c_int(q.stride(0)), _ptr(k), c_int(k.stride(0)), c_int(heads_per_qk), _ptr(v), c_int(v.stride(0)),
         _ptr(dt_dec), _ptr(decay_head), _ptr(skip), _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(out),
@@ -1202,11 +1229,23 @@ def attn_sink_tc(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, seq_q_
           and out.is_contiguous() and tuple(out.shape) == (T, n_heads * vdim), "attn_sink_tc: q and out")
     _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (n_kv_heads, page_size, dim + vdim), "attn_sink_tc: cache rows")
     _need(sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == n_heads), "attn_sink_tc: sinks float32 [heads]")
+    # single tokens: with few requests a request's 64-key tiles are shared out among blocks until the SMs are covered
+    # twice (a function of the step's shape only: the same step replays from a graph)
+    splits, part = 1, None
+    if singles:
+        from tokasaurus_b200.kernels.device import device_limits
+
+        blocks = n_seqs * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16)
+        splits = max(1, min(8, (2 * device_limits(q.device).sm_count) // max(1, blocks)))
+        if window:
+            splits = min(splits, max(1, (window + 63) // 64))
+        if splits > 1:
+            part = torch.empty((n_seqs * n_heads * splits * (vdim + 2),), dtype=torch.float32, device=q.device)
     _check(_fn(_libs.get("attention_sink.cu", **sink_attention_defines(dim, vdim)), "tkb_attn_sink_tc_bf16")(
         _ptr(q), _ptr(out), _ptr(cache), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(page_indptr),
         _ptr(page_ids), c_int(T), c_int(n_seqs), c_int(1 if portions else 0), c_int(1 if singles else 0), _ptr(sinks),
         c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale), c_float(softcap or 0.0), c_int(window or 0),
-        c_int(cache.shape[0]), _ptr(status), _stream()), "attn_sink_tc")
+        c_int(cache.shape[0]), _ptr(status), _ptr(part), c_int(splits), _stream()), "attn_sink_tc")
 
 
 def prepare_modules(modules) -> None:

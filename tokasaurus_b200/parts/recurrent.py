@@ -85,7 +85,7 @@ class DecayedLinearAttention(Mixer):
         self.norm_eps = float(norm_eps)
         self.names = dict(q=q_name, k=k_name, v=v_name, g=g_name, norm=norm_name, o=o_name)
         self.defines = ops.decay_recurrence_defines(dim, vdim)  # refuses sizes the kernel does not take
-        self.defines_single = ops.decay_recurrence_defines(dim, vdim, single=True)
+        self.walk_builds = ops.decay_walk_modules(dim, vdim)
 
     def weight_specs(self):
         n, H, d, e = self.names, self.n_heads, self.dim, self.vdim
@@ -94,7 +94,7 @@ class DecayedLinearAttention(Mixer):
                 WeightSpec(n["o"], (self.width, H * e)), WeightSpec(n["norm"], (H * e,), role="vector"))
 
     def kernel_modules(self, dtype):
-        return (("decay_recurrence.cu", self.defines), ("decay_recurrence.cu", self.defines_single), ("post_norm.cu", None))
+        return tuple(("decay_recurrence.cu", d) for d in self.walk_builds) + (("post_norm.cu", None),)
 
     def cache_need(self):
         return StateNeed((self.n_heads * self.vdim * self.dim,), "float32")  # S^T: [head][value][key channel]
@@ -115,7 +115,7 @@ class DecayedLinearAttention(Mixer):
         ops.silu_cols(proj, 2 * H * d + H * e, self.defines)  # q, k and v, in place
         raw = torch.empty((T, H * e), dtype=torch.float32, device=h.device)
         ops.decay_walk(q, k, v, 1, None, self.decay_t, None, cache.state, raw, ctx.seq_slot, ctx.seq_q_start,
-                       ctx.seq_q_len, ctx.n_seqs, H, d, e, self.defines, cache.writable)
+                       ctx.seq_q_len, ctx.n_seqs, H, d, e, cache.writable)
         if out_rows is not None:
             raw, g = _rows(raw, out_rows), _rows(g.contiguous(), out_rows)
         o = torch.empty(raw.shape, dtype=h.dtype, device=h.device)

@@ -41,7 +41,7 @@ class SelectiveStateSpace(Mixer):
         self.names = dict(w_in=in_name, conv=conv_name, conv_b=conv_bias_name, dt_bias=dt_bias_name, a_log=a_log_name,
                           d=d_name, norm=norm_name, o=o_name)
         self.defines = ops.decay_recurrence_defines(state, vdim)
-        self.defines_single = ops.decay_recurrence_defines(state, vdim, single=True)
+        self.walk_builds = ops.decay_walk_modules(state, vdim)
 
     def weight_specs(self):
         n, H = self.names, self.n_heads
@@ -53,7 +53,7 @@ class SelectiveStateSpace(Mixer):
                 WeightSpec(n["o"], (self.width, self.inner)))
 
     def kernel_modules(self, dtype):
-        return (("decay_recurrence.cu", self.defines), ("decay_recurrence.cu", self.defines_single), ("post_norm.cu", None))
+        return tuple(("decay_recurrence.cu", d) for d in self.walk_builds) + (("post_norm.cu", None),)
 
     def cache_need(self):
         # [S^T of every head: heads x vdim x state | the convolution's last taps - 1 inputs: (taps - 1) x channels]
@@ -79,7 +79,7 @@ class SelectiveStateSpace(Mixer):
         raw = torch.empty((T, inner), dtype=torch.float32, device=h.device)
         ops.decay_walk(xbc[:, inner + G * N:], xbc[:, inner:inner + G * N], xbc[:, :inner], H // G, dt_dec, None,
                        self.d_skip, cache.state, raw, ctx.seq_slot, ctx.seq_q_start, ctx.seq_q_len, ctx.n_seqs, H, N, P,
-                       self.defines, cache.writable)
+                       cache.writable)
         z = proj[:, :inner]
         if out_rows is not None:
             raw, z = _rows(raw, out_rows), _rows(z.contiguous(), out_rows)
