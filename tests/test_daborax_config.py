@@ -57,6 +57,16 @@ def test_description_follows_the_configuration():
     assert model.blocks[0].mult == 0.6 and model.embedding.scale == 3.5 and model.blocks[2].ffn.limit == 0.8
 
 
+def test_a_layer_may_name_a_layer_that_borrows_itself():
+    d = base_config()
+    d["layers"].append(dict(copy.deepcopy(d["layers"][3]), weights_of=3))  # layer 3 runs with layer 1's tensors
+    arch = lookup_architecture(d)
+    cfg = arch.parse_config(d)
+    assert cfg.layers[5].weights_of == 1
+    model = arch.build_model(cfg)
+    assert [c.block for c in model.run_order] == [0, 1, 2, 1, 0, 1] and len({c.cache for c in model.run_order}) == 6
+
+
 def test_defaults():
     d = base_config()
     d.pop("residual_mult")
@@ -75,7 +85,6 @@ def test_defaults():
 
 @pytest.mark.parametrize("change,word", [
     (lambda d: d["layers"][3].update(weights_of=2), "weights_of"),
-    (lambda d: d["layers"][4].update(weights_of=3), "weights_of"),
     (lambda d: d["layers"][3].update(weights_of=7), "weights_of"),
     (lambda d: d["layers"][1]["mixer"].update(groups=3), "groups"),
     (lambda d: d["layers"][1]["mixer"].update(norm_groups=5), "norm groups"),

@@ -42,14 +42,14 @@ def ops():
 def test_sinusoidal_positions(ops, H):
     from tokasaurus_b200.parts import SinusoidalPositions
 
-    pos = [0, 1, 2, 17, 500, 4095, 3]
+    pos = [0, 1, 2, 17, 500, 4095, 3, 100000]
     x0 = torch.randn(len(pos), H)
     x = x0.to(DEV)
     ops.add_sinusoid(x, i32(pos), SinusoidalPositions(H).inv_freq().to(DEV))
     want = x0.double().clone()
     for r, p in enumerate(pos):
         want[r] += plain.position_vectors(1, H, start=p)[0]
-    assert float((x.cpu().double() - want).abs().max()) < 3e-4  # the angle p * f is a float32 product
+    assert float((x.cpu().double() - want).abs().max()) < 5e-7  # angles in float64: only the float32 sum is rounded
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -245,7 +245,7 @@ def paged(n_tokens, page, seed):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("dim,vdim,page,heads,kv", [(64, 48, 16, 6, 2), (24, 40, 8, 3, 3), (20, 6, 16, 4, 1), (128, 128, 16, 2, 1)])
+@pytest.mark.parametrize("dim,vdim,page,heads,kv", [(64, 48, 16, 6, 2), (24, 40, 8, 3, 3), (20, 6, 16, 4, 1), (128, 128, 16, 2, 1), (32, 16, 16, 20, 1)])
 def test_sink_attention_window_edges(ops, dtype, dim, vdim, page, heads, kv):
     """One made-up key that a probe query scores far above all others, with a value that stands out, at a page's first
     and last slot: seen from the position just inside the window and not from the one just outside, inside a portion

@@ -159,8 +159,11 @@ class DaboraxConfig:
                                        ClampedFeedForwardConfig.from_dict(ld.get("mlp"), where + ".mlp"), ld.get("weights_of"))
             j = layer.weights_of
             if j is not None:
-                if not isinstance(j, int) or isinstance(j, bool) or not 0 <= j < i or layers[j].weights_of is not None:
-                    raise ConfigError(f"{where}.weights_of={j!r} must name an earlier layer that has tensors of its own")
+                if not isinstance(j, int) or isinstance(j, bool) or not 0 <= j < i:
+                    raise ConfigError(f"{where}.weights_of={j!r} must name an earlier layer")
+                if layers[j].weights_of is not None:  # a layer that itself borrows: the tensors are its lender's
+                    j = layers[j].weights_of
+                    layer = DaboraxLayerConfig(layer.type, layer.mixer, layer.mlp, j)
                 if layers[j].type != layer.type or (layers[j].mlp is None) != (layer.mlp is None):
                     raise ConfigError(f"{where}.weights_of={j}: layer {j} has another mixer type or feed-forward")
             layers.append(layer)

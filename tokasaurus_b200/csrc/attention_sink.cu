@@ -15,7 +15,7 @@
 // sums output elements d, d + 32, ...  Scores, weights and sums are float32.
 //
 //
-// In bfloat16, for key sizes that are multiples of 16 and value sizes that are multiples of 16, two tensor-core kernels
+// In bfloat16, for key and value sizes that are multiples of 16 up to 256, two tensor-core kernels
 // (mma.sync m16n8k16, float32 scores, weights rounded to bfloat16 for their product with the values) take the place of
 // the FP32-pipe kernel.  Both stage 64 cached rows at a time in shared memory (cp.async, two buffers; a row's key and
 // value arrive in one copy) and keep a running softmax that the sink opens.  attn_sink_tiles: a block owns 64 queries
@@ -250,7 +250,7 @@ TKB_SINK_EXPORTS(f32, float)
 TKB_SINK_EXPORTS(bf16, __nv_bfloat16)
 
 // ------------------------------------------------------------------------------------------------ tensor cores
-#if (TKB_QK % 16 == 0) && (TKB_VD % 16 == 0)
+#if (TKB_QK % 16 == 0) && (TKB_VD % 16 == 0) && (TKB_QK <= 256) && (TKB_VD <= 256)
 #define TKB_SINK_TC 1
 namespace {
 

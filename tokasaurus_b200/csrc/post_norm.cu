@@ -4,7 +4,7 @@
 //   scaled_norm_add   x += mult * scale[c] * w[c] * (y + bias)[c] / sqrt(mean((y + bias)^2) + eps)   (x float32, in
 //                     place), and the new x in the activation type for the sublayer that reads it next
 //   cast_rows         float32 rows in the activation type
-//   add_sinusoid      x[t][2i] += sin(p_t * f_i),  x[t][2i+1] += cos(p_t * f_i)   (f_i a float32 table)
+//   add_sinusoid      x[t][2i] += sin(p_t * f_i),  x[t][2i+1] += cos(p_t * f_i)   (f_i a float64 table)
 //   clamped_glu       g = min(gate, L), u = clamp(up, -L, L), out = g * sigmoid(alpha * g) * (u + 1)
 //   gated_group_norm  a row of float32 values, gated and RMS-normed in equal parts:
 //                       mode 0: out = N(y) * w * sigmoid(gate)        (the norm first)
@@ -57,17 +57,19 @@ __global__ void cast_rows_kernel(const float* __restrict__ x, T* __restrict__ ou
     out[i] = from_float<T>(x[i]);
 }
 
+// Frequencies, angle, sine and cosine in float64 (a float32 product of a position in the thousands and a frequency is off
+// by 1e-4 of a radian); what is added to the row is their float32 rounding.
 __global__ void add_sinusoid_kernel(float* __restrict__ x, const int* __restrict__ positions,
-                                    const float* __restrict__ freq, int H) {
+                                    const double* __restrict__ freq, int H) {
   trigger_dependents();
   grid_dependency_wait();
-  const float p = (float)positions[blockIdx.x];
+  const double p = (double)positions[blockIdx.x];
   float* row = x + (size_t)blockIdx.x * H;
   for (int i = threadIdx.x; 2 * i < H; i += blockDim.x) {
-    float s, c;
-    sincosf(p * freq[i], &s, &c);
-    row[2 * i] += s;
-    if (2 * i + 1 < H) row[2 * i + 1] += c;
+    double s, c;
+    sincos(p * freq[i], &s, &c);
+    row[2 * i] += (float)s;
+    if (2 * i + 1 < H) row[2 * i + 1] += (float)c;
   }
 }
 
@@ -149,7 +151,7 @@ gated_group_norm_kernel(const float* __restrict__ y, int y_stride, const float* 
 TKB_POST_NORM_EXPORTS(f32, float)
 TKB_POST_NORM_EXPORTS(bf16, __nv_bfloat16)
 
-TKB_EXPORT int tkb_add_sinusoid(float* x, const int* positions, const float* freq, int rows, int H, void* st) {
+TKB_EXPORT int tkb_add_sinusoid(float* x, const int* positions, const double* freq, int rows, int H, void* st) {
   if (rows <= 0) return 0;
   return launch_pdl(add_sinusoid_kernel, dim3(rows), dim3(row_threads(H * 2)), 0, (cudaStream_t)st, x, positions,
                     freq, H);

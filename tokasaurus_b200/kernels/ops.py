@@ -1020,12 +1020,12 @@ def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def add_sinusoid(x: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor) -> None:
-    """x[t, 2i] += sin(positions[t] * freq[i]), x[t, 2i + 1] += cos(same); x float32, angles float32."""
+    """x[t, 2i] += sin(positions[t] * freq[i]), x[t, 2i + 1] += cos(same); x float32, frequencies and angles float64."""
     _need_cuda(x, positions, freq)
     rows, H = x.shape
     _need(x.dtype == torch.float32 and x.is_contiguous(), "add_sinusoid: x contiguous float32")
     _need(positions.dtype == torch.int32 and positions.numel() >= rows, "add_sinusoid: positions int32 [T]")
-    _need(freq.dtype == torch.float32 and freq.is_contiguous() and freq.numel() == (H + 1) // 2, "add_sinusoid: float32 [ceil(H / 2)] frequencies")
+    _need(freq.dtype == torch.float64 and freq.is_contiguous() and freq.numel() == (H + 1) // 2, "add_sinusoid: float64 [ceil(H / 2)] frequencies")
     _check(_fn(_libs.get("post_norm.cu"), "tkb_add_sinusoid")(_ptr(x), _ptr(positions), _ptr(freq), c_int(rows), c_int(H),
                                                               _stream()), "add_sinusoid")
 
@@ -1211,8 +1211,9 @@ def attn_sink(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, token_seq
 
 
 def can_use_attn_sink_tc(dtype: torch.dtype, dim: int, vdim: int) -> bool:
-    """The tensor-core kernels of csrc/attention_sink.cu take bfloat16 rows whose key and value sizes are multiples of 16."""
-    return dtype == torch.bfloat16 and dim % 16 == 0 and vdim % 16 == 0 and dim + vdim <= 512
+    """The tensor-core kernels of csrc/attention_sink.cu take bfloat16 rows whose key and value sizes are multiples of 16
+    up to 256."""
+    return dtype == torch.bfloat16 and dim % 16 == 0 and vdim % 16 == 0 and dim <= 256 and vdim <= 256
 
 
 def attn_sink_tc(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, seq_q_start: torch.Tensor, seq_q_len: torch.Tensor,

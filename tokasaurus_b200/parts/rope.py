@@ -69,8 +69,8 @@ class RotaryEncoding(PositionEncoding):
 
 class SinusoidalPositions(PositionEncoding):
     """A position vector added to the embedding: entry 2i is sin(p * base^(-2i / width)), entry 2i + 1 the cosine of
-    the same angle.  The frequencies are worked out in float64 and kept as float32; the angle is their float32
-    product with the position, formed in the kernel."""
+    the same angle.  Frequencies, angles, sines and cosines are float64 (the kernel forms the angle as the product of
+    position and frequency); what is added to the float32 stream is their rounding."""
 
     kind = "additive"
     rotary_dim = 0
@@ -80,6 +80,6 @@ class SinusoidalPositions(PositionEncoding):
         self.base = float(base)
 
     def inv_freq(self) -> torch.Tensor:
-        """float32 [ceil(width / 2)], on the CPU."""
+        """float64 [ceil(width / 2)], on the CPU."""
         i = torch.arange((self.width + 1) // 2, dtype=torch.float64)
-        return (self.base ** (-2.0 * i / self.width)).to(torch.float32)
+        return self.base ** (-2.0 * i / self.width)
