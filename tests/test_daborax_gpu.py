@@ -83,6 +83,28 @@ def test_clamped_gated_unit(ops, dtype):
         ops.clamped_glu(gu.to(DEV), out, limit, 1.702)
         assert rel_err(out.float().cpu(), want) < TOL[dtype]
     assert float(gu.abs().max()) > 2.5  # both limits cut something
+    # gate and up columns interleaved in groups of 8 (the layout of the stacked weights in bfloat16): 56 features
+    gu = (torch.randn(9, 2 * 56, generator=g) * 2).to(DT[dtype])
+    gg, uu = gu[:, :56].double().clamp(max=1.5), gu[:, 56:].double().clamp(-1.5, 1.5)
+    mixed = torch.stack([gu[:, :56].reshape(9, 7, 8), gu[:, 56:].reshape(9, 7, 8)], dim=2).reshape(9, 112).contiguous()
+    out = torch.empty(9, 56, dtype=DT[dtype], device=DEV)
+    ops.clamped_glu(mixed.to(DEV), out, 1.5, 1.702, interleave=8)
+    assert rel_err(out.float().cpu(), gg * torch.sigmoid(1.702 * gg) * (uu + 1)) < TOL[dtype]
+
+
+@pytest.mark.parametrize("M,K,inner", [(300, 192, 200), (128, 64, 40), (1000, 512, 1024)])
+def test_clamped_unit_in_the_tensor_core_product(ops, M, K, inner):
+    """The gated tcgen05 product with the clamped unit as its epilogue against the plain statement."""
+    g = torch.Generator().manual_seed(M)
+    a = (torch.randn(M, K, generator=g)).to(torch.bfloat16)
+    wg, wu = (torch.randn(inner, K, generator=g) * 0.1).to(torch.bfloat16), (torch.randn(inner, K, generator=g) * 0.1).to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    got = ops.gemm_tcgen05_clamped(a.to(DEV), ops.interleave_gate_up(wg.to(DEV), wu.to(DEV)), status, 0.9, 1.702)
+    gg = (a.double() @ wg.double().T).clamp(max=0.9)
+    uu = (a.double() @ wu.double().T).clamp(-0.9, 0.9)
+    assert int(status.item()) == 0
+    assert float(((a.double() @ wg.double().T) > 0.9).double().mean()) > 0.05  # the limit cuts something
+    assert rel_err(got.float().cpu(), gg * torch.sigmoid(1.702 * gg) * (uu + 1)) < TOL["bfloat16"]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -41,7 +41,7 @@ template <int BN, bool GATED>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     bf16* __restrict__ out, int ldo, int M, int N, int K, int* __restrict__ status,
-                    const int* __restrict__ tile_group, int group_rows) {
+                    const int* __restrict__ tile_group, int group_rows, float act_limit, float act_alpha) {
   extern __shared__ unsigned char smem_raw[];
   constexpr int STAGES = Cfg<BN>::STAGES;
   __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
@@ -172,7 +172,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 float y[8];
 #pragma unroll
                 for (int jj = 0; jj < 8; jj++)
-                  y[jj] = silu_mul_fast(__uint_as_float(r[16 * g + jj]), __uint_as_float(r[16 * g + 8 + jj]));
+                  y[jj] = act_limit > 0.f
+                              ? clamped_glu_fast(__uint_as_float(r[16 * g + jj]), __uint_as_float(r[16 * g + 8 + jj]),
+                                                 act_limit, act_alpha)
+                              : silu_mul_fast(__uint_as_float(r[16 * g + jj]), __uint_as_float(r[16 * g + 8 + jj]));
                 uint4 u;
                 u.x = pack_bf16(y[0], y[1]);
                 u.y = pack_bf16(y[2], y[3]);
@@ -207,7 +210,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 template <int BN, bool GATED>
 int launch(const void* A, int lda, const void* W, int ldw, void* out, int ldo, int M, int N, int K, int* status,
-           cudaStream_t st, const int* tile_group = nullptr, int groups = 1) {
+           cudaStream_t st, const int* tile_group = nullptr, int groups = 1, float act_limit = 0.f,
+           float act_alpha = 0.f) {
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -224,7 +228,7 @@ int launch(const void* A, int lda, const void* W, int ldw, void* out, int ldo, i
   const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
   dim3 grid(tiles < n_sms ? tiles : n_sms);
   gemm_tcgen05_kernel<BN, GATED><<<grid, THREADS, Cfg<BN>::SMEM_BYTES, st>>>(map_a, map_w, (bf16*)out, ldo, M, N, K, status,
-                                                                                 tile_group, N);
+                                                                                 tile_group, N, act_limit, act_alpha);
   return launch_status();
 }
 
@@ -247,6 +251,20 @@ TKB_EXPORT int tkb_gemm_tcgen05_bf16(const void* A, int lda, const void* W, int 
   }
   return gated ? launch<128, true>(A, lda, W, ldw, out, ldo, M, N, K, status, st)
                : launch<128, false>(A, lda, W, ldw, out, ldo, M, N, K, status, st);
+}
+
+// The gated form with another activation in its epilogue: g = min(gate, limit), u = clamp(up, -limit, limit),
+// out = g * sigmoid(alpha * g) * (u + 1) (limit > 0).
+TKB_EXPORT int tkb_gemm_tcgen05_clamped_bf16(const void* A, int lda, const void* W, int ldw, void* out, int ldo, int M,
+                                             int N, int K, float limit, float alpha, int* status, void* st_) {
+  cudaStream_t st = (cudaStream_t)st_;
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K & 7) || (lda & 7) || (ldw & 7) || (((uintptr_t)A) & 15) || (((uintptr_t)W) & 15)) return -2;
+  if ((N & 15) || !(limit > 0.f)) return -2;
+  int rc = get_encode();
+  if (rc) return rc;
+  if (N >= 256) return launch<256, true>(A, lda, W, ldw, out, ldo, M, N, K, status, st, nullptr, 1, limit, alpha);
+  return launch<128, true>(A, lda, W, ldw, out, ldo, M, N, K, status, st, nullptr, 1, limit, alpha);
 }
 
 // Grouped form: W is [groups * N, K], rows g * N .. (g + 1) * N the weights of group g, and row tile i of A (128

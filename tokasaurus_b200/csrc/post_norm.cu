@@ -73,16 +73,19 @@ __global__ void add_sinusoid_kernel(float* __restrict__ x, const int* __restrict
   }
 }
 
+// interleave 0: a row is [gate | up]; 8: columns in groups of 16, 8 gate columns then the 8 up columns of the same features
 template <typename TI, typename TO>
 __global__ void clamped_glu_kernel(const TI* __restrict__ gate_up, TO* __restrict__ out, int inner, float limit,
-                                   float alpha) {
+                                   float alpha, int interleave) {
   trigger_dependents();
   grid_dependency_wait();
   const TI* row = gate_up + (size_t)blockIdx.x * 2 * inner;
   TO* orow = out + (size_t)blockIdx.x * inner;
   for (int i = threadIdx.x; i < inner; i += blockDim.x) {
-    const float g = fminf(to_float(row[i]), limit);
-    const float u = fminf(fmaxf(to_float(row[inner + i]), -limit), limit);
+    const int gi = interleave ? ((i >> 3) << 4) + (i & 7) : i;
+    const int ui = interleave ? gi + 8 : inner + i;
+    const float g = fminf(to_float(row[gi]), limit);
+    const float u = fminf(fmaxf(to_float(row[ui]), -limit), limit);
     orow[i] = from_float<TO>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
   }
 }
@@ -159,11 +162,12 @@ TKB_EXPORT int tkb_add_sinusoid(float* x, const int* positions, const double* fr
 
 // gate_up [rows, 2 * inner] (gate columns, then up columns) in the activation type or float32; out [rows, inner]
 #define TKB_GLU_EXPORT(NAME, TI, TO)                                                                                  \
-  TKB_EXPORT int NAME(const void* gate_up, void* out, int rows, int inner, float limit, float alpha, void* st) {      \
+  TKB_EXPORT int NAME(const void* gate_up, void* out, int rows, int inner, float limit, float alpha, int interleave,  \
+                      void* st) {                                                                                     \
     if (rows <= 0) return 0;                                                                                          \
-    if (inner <= 0) return -2;                                                                                        \
+    if (inner <= 0 || (interleave != 0 && (interleave != 8 || inner % 8))) return -2;                                 \
     return launch_pdl(clamped_glu_kernel<TI, TO>, dim3(rows), dim3(row_threads(inner * 4)), 0, (cudaStream_t)st,      \
-                      (const TI*)gate_up, (TO*)out, inner, limit, alpha);                                             \
+                      (const TI*)gate_up, (TO*)out, inner, limit, alpha, interleave);                                 \
   }
 TKB_GLU_EXPORT(tkb_clamped_glu_f32_f32, float, float)
 TKB_GLU_EXPORT(tkb_clamped_glu_f32_bf16, float, __nv_bfloat16)

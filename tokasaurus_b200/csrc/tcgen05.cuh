@@ -104,6 +104,15 @@ __device__ __forceinline__ float silu_mul_fast(float g, float u) {
   return __fdividef(g * u, 1.f + e);
 }
 
+// g' * sigmoid(alpha g') * (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit)
+__device__ __forceinline__ float clamped_glu_fast(float g, float u, float limit, float alpha) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-alpha * g * 1.4426950408889634f));
+  return __fdividef(g * (u + 1.f), 1.f + e);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);

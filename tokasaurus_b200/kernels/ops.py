@@ -620,6 +620,23 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, gated: 
     return out
 
 
+def gemm_tcgen05_clamped(a: torch.Tensor, w_interleaved: torch.Tensor, status: torch.Tensor, limit: float,
+                         alpha: float) -> torch.Tensor:
+    """The gated tcgen05 product with the clamped unit in its epilogue: ``w_interleaved`` interleaves gate and up rows
+    (``interleave_gate_up``); the result is g * sigmoid(alpha g) * (u + 1) [M, N / 2] with g = min(gate, limit),
+    u = clamp(up, -limit, limit), taken from the float32 accumulators."""
+    _need_cuda(a, w_interleaved, status)
+    _need(can_use_tcgen05(a, w_interleaved), "gemm_tcgen05_clamped: bfloat16 operands, K and strides multiples of 8, 16-byte aligned")
+    M, K = a.shape
+    N = w_interleaved.shape[0]
+    _need(w_interleaved.shape[1] == K and N % 16 == 0 and limit > 0, "gemm_tcgen05_clamped: shapes, a positive limit")
+    out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=a.device)
+    _check(_fn(_libs.get("gemm_tcgen05.cu"), "tkb_gemm_tcgen05_clamped_bf16")(
+        _ptr(a), c_int(a.stride(0)), _ptr(w_interleaved), c_int(w_interleaved.stride(0)), _ptr(out), c_int(out.stride(0)),
+        c_int(M), c_int(N), c_int(K), c_float(limit), c_float(alpha), _ptr(status), _stream()), "gemm_tcgen05_clamped")
+    return out
+
+
 TC_DECODE_M_MAX = 64
 
 
@@ -1030,9 +1047,10 @@ def add_sinusoid(x: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor) -
                                                               _stream()), "add_sinusoid")
 
 
-def clamped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> None:
+def clamped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float, interleave: int = 0) -> None:
     """out = g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit);
-    gate_up [rows, 2 * inner] = [gate | up] in out's type or float32."""
+    gate_up [rows, 2 * inner] in out's type or float32: [gate | up], or with ``interleave`` 8 columns in groups of 16,
+    8 gate columns then the 8 up columns of the same features (``interleave_gate_up``)."""
     _need_cuda(gate_up, out)
     rows, two_i = gate_up.shape
     _need(two_i % 2 == 0 and tuple(out.shape) == (rows, two_i // 2) and gate_up.is_contiguous() and out.is_contiguous(),
@@ -1040,7 +1058,7 @@ def clamped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: f
     _need(gate_up.dtype in (torch.float32, out.dtype), "clamped_glu: gate_up float32 or in out's type")
     name = f"tkb_clamped_glu_{_suffix(gate_up.dtype)}_{_suffix(out.dtype)}"
     _check(_fn(_libs.get("post_norm.cu"), name)(_ptr(gate_up), _ptr(out), c_int(rows), c_int(two_i // 2), c_float(limit),
-                                                c_float(alpha), _stream()), "clamped_glu")
+                                                c_float(alpha), c_int(interleave), _stream()), "clamped_glu")
 
 
 def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, groups: int,

@@ -61,8 +61,9 @@ class GatedMLP(FeedForward):
 
 class ClampedGLU(FeedForward):
     """``down(g * sigmoid(alpha * g) * (u + 1))`` with ``g = min(gate(h), limit)`` and ``u = clamp(up(h), -limit,
-    limit)``; no biases.  The gate and up matrices are stacked into one product; the update leaves as float32 (a norm
-    reads it)."""
+    limit)``; no biases.  The gate and up matrices are stacked into one product (in bfloat16 with their rows
+    interleaved in groups of 8, the layout whose tcgen05 product applies the unit in its epilogue: steps of many rows
+    have no activation pass over memory); the update leaves as float32 (a norm reads it)."""
 
     def __init__(self, width: int, inner: int, limit: float, gate_name: str, up_name: str, down_name: str,
                  alpha: float = 1.702):
@@ -75,17 +76,25 @@ class ClampedGLU(FeedForward):
                 WeightSpec(d, (self.width, self.inner)))
 
     def kernel_modules(self, dtype):
-        return (("post_norm.cu", None),)
+        return (("post_norm.cu", None),) + ((("gemm_tcgen05.cu", None),) if dtype == "bfloat16" else ())
 
     def bind(self, weights, rt) -> None:
         g, u, d = self.names
-        self.w_gate_up = torch.cat([weights[g], weights[u]], dim=0).contiguous()
+        self.interleave = 8 if (rt.dtype == torch.bfloat16 and self.inner % 8 == 0) else 0
+        if self.interleave:
+            self.w_gate_up = ops.interleave_gate_up(weights[g], weights[u])
+        else:
+            self.w_gate_up = torch.cat([weights[g], weights[u]], dim=0).contiguous()
         self.w_down = weights[d].contiguous()
 
     def forward(self, ctx, h):
-        gu = ops.linear(h, self.w_gate_up)
-        act = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
-        ops.clamped_glu(gu, act, self.limit, self.alpha)
+        if self.interleave and h.shape[0] >= ops.TCGEN05_M_MIN and ops.can_use_tcgen05(h, self.w_gate_up):
+            status = ctx.status if ctx is not None else torch.zeros(1, dtype=torch.int32, device=h.device)
+            act = ops.gemm_tcgen05_clamped(h, self.w_gate_up, status, self.limit, self.alpha)
+        else:
+            gu = ops.linear(h, self.w_gate_up)
+            act = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
+            ops.clamped_glu(gu, act, self.limit, self.alpha, self.interleave)
         return ops.linear(act, self.w_down, out_dtype=torch.float32)
 
 
