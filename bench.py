@@ -161,7 +161,7 @@ def prefill_flops(m: dict, T: int, rows: int = 1) -> float:
 
 
 TIMED_OPS = ("scaled_norm_add", "cast_rows", "add_sinusoid", "clamped_glu", "gated_group_norm", "ssm_prep", "decay_walk",
-             "sink_attn_prep", "attn_sink", "attn_sink_tc", "silu_cols", "add_layernorm", "add_layernorm_conv1", "short_conv", "polynorm", "gated_recurrence", "latent_prep",
+             "sink_attn_prep", "attn_sink", "attn_sink_tc", "silu_cols", "gemm_tcgen05_clamped", "add_layernorm", "add_layernorm_conv1", "short_conv", "polynorm", "gated_recurrence", "latent_prep",
              "rotate_pairs", "latent_attn", "moe_route", "moe_order", "moe_gather", "moe_gemm", "moe_combine",
              "gemm_tcgen05_grouped", "embed_gather", "add_rmsnorm", "rope_kv_write", "rope_kv_write_partials", "linear_decode", "linear_smallm",
              "linear_smallm_gated", "silu_mul", "gather_rows", "attn_decode_mma", "attn_decode_rope_mma", "attn_prefill_mma",

@@ -70,6 +70,11 @@ def test_output_norm_with_scale_and_residual_add(ops, dtype, H):
     xd = x.to(DEV)
     ops.scaled_norm_add(xd, y.to(DEV), w.to(DEV), None, 1.0, 1e-6)  # no layer scale, multiplier 1
     assert rel_err(xd.cpu(), x.double() + plain.rms_norm(y.double(), w.double(), 1e-6)) < 1e-6
+    sl = torch.randn(3, 5, H, generator=g) * 0.2  # float32 slices of a split product instead
+    xd = x.to(DEV)
+    ops.scaled_norm_add(xd, sl.to(DEV), w.to(DEV), ls.to(DEV), 0.6, 1e-6, None, b.to(DEV))
+    want = x.double() + 0.6 * plain.rms_norm(sl.double().sum(0) + b.double(), w.double(), 1e-6) * ls.double()
+    assert rel_err(xd.cpu(), want) < 1e-6
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

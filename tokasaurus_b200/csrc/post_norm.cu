@@ -2,7 +2,8 @@
 // such models bring along:
 //
 //   scaled_norm_add   x += mult * scale[c] * w[c] * (y + bias)[c] / sqrt(mean((y + bias)^2) + eps)   (x float32, in
-//                     place), and the new x in the activation type for the sublayer that reads it next
+//                     place), and the new x in the activation type for the sublayer that reads it next; y whole
+//                     rows or the float32 slices of a K-split product
 //   cast_rows         float32 rows in the activation type
 //   add_sinusoid      x[t][2i] += sin(p_t * f_i),  x[t][2i+1] += cos(p_t * f_i)   (f_i a float64 table)
 //   clamped_glu       g = min(gate, L), u = clamp(up, -L, L), out = g * sigmoid(alpha * g) * (u + 1)
@@ -25,22 +26,28 @@ inline int row_threads(int n) {
 
 template <typename T>
 __global__ void __launch_bounds__(512)
-scaled_norm_add_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ bias,
-                       const float* __restrict__ w, const float* __restrict__ scale, float mult, float eps,
-                       T* __restrict__ h_out, int H) {
+scaled_norm_add_kernel(float* __restrict__ x, const float* __restrict__ y, int n_slices, long long slice_stride,
+                       const float* __restrict__ bias, const float* __restrict__ w, const float* __restrict__ scale,
+                       float mult, float eps, T* __restrict__ h_out, int H) {
   __shared__ float red[33];
   trigger_dependents();
   grid_dependency_wait();
   const size_t row = (size_t)blockIdx.x * H;
+  // y may arrive as the float32 slices of a K-split product: they are added in slice order, both times alike
+  auto value = [&](int c) {
+    float v = y[row + c];
+    for (int s = 1; s < n_slices; s++) v += y[(size_t)s * slice_stride + row + c];
+    return v + (bias ? bias[c] : 0.f);
+  };
   float ss = 0.f;
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
-    const float v = y[row + c] + (bias ? bias[c] : 0.f);
+    const float v = value(c);
     ss = fmaf(v, v, ss);
   }
   ss = block_sum(ss, red);
   const float r = rsqrtf(ss / (float)H + eps);
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
-    const float v = y[row + c] + (bias ? bias[c] : 0.f);
+    const float v = value(c);
     float u = v * r * w[c];
     if (scale) u *= scale[c];
     const float nx = fmaf(mult, u, x[row + c]);
@@ -126,13 +133,13 @@ gated_group_norm_kernel(const float* __restrict__ y, int y_stride, const float* 
 }  // namespace
 
 #define TKB_POST_NORM_EXPORTS(SUF, T)                                                                                 \
-  TKB_EXPORT int tkb_scaled_norm_add_##SUF(float* x, const float* y, const float* bias, const float* w,               \
-                                           const float* scale, float mult, float eps, void* h_out, int rows, int H,   \
-                                           void* st) {                                                                \
+  TKB_EXPORT int tkb_scaled_norm_add_##SUF(float* x, const float* y, int n_slices, long long slice_stride,            \
+                                           const float* bias, const float* w, const float* scale, float mult,         \
+                                           float eps, void* h_out, int rows, int H, void* st) {                       \
     if (rows <= 0) return 0;                                                                                          \
-    if (H <= 0) return -2;                                                                                            \
-    return launch_pdl(scaled_norm_add_kernel<T>, dim3(rows), dim3(row_threads(H)), 0, (cudaStream_t)st, x, y, bias,   \
-                      w, scale, mult, eps, (T*)h_out, H);                                                             \
+    if (H <= 0 || n_slices < 1) return -2;                                                                            \
+    return launch_pdl(scaled_norm_add_kernel<T>, dim3(rows), dim3(row_threads(H)), 0, (cudaStream_t)st, x, y,         \
+                      n_slices, slice_stride, bias, w, scale, mult, eps, (T*)h_out, H);                               \
   }                                                                                                                   \
   TKB_EXPORT int tkb_cast_rows_##SUF(const float* x, void* out, long long n, void* st) {                              \
     if (n <= 0) return 0;                                                                                             \

@@ -1012,11 +1012,13 @@ def moe_combine(y: torch.Tensor, place_of: torch.Tensor, top_w: torch.Tensor, sh
 def scaled_norm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor | None, mult: float,
                     eps: float, h_out: torch.Tensor | None = None, bias: torch.Tensor | None = None) -> None:
     """x += mult * scale * weight * N(y + bias) in place (x, y float32; N divides a row by its root mean square);
-    ``h_out`` (activation type, x's shape) receives the new x."""
+    ``h_out`` (activation type, x's shape) receives the new x.  ``y``: [rows, H], or [slices, rows, H], the slices of
+    a split matrix product (``linear_few_rows``), added in slice order."""
     _need_cuda(x, y, weight, scale, h_out, bias)
     rows, H = x.shape
+    n_slices = y.shape[0] if y.dim() == 3 else 1
     _need(x.dtype == torch.float32 and x.is_contiguous() and y.dtype == torch.float32 and y.is_contiguous()
-          and y.shape == x.shape, "scaled_norm_add: x and y contiguous float32 of one shape")
+          and tuple(y.shape[-2:]) == (rows, H), "scaled_norm_add: x and y contiguous float32 of one shape")
     for v, what in ((weight, "norm weight"), (scale, "scale"), (bias, "bias")):
         _need(v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == H),
               f"scaled_norm_add: {what} float32 [H]")
@@ -1024,8 +1026,18 @@ def scaled_norm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, scal
     _need(h_out is None or (h_out.shape == x.shape and h_out.is_contiguous()), "scaled_norm_add: h_out of x's shape")
     suf = _suffix(h_out.dtype) if h_out is not None else "f32"
     _check(_fn(_libs.get("post_norm.cu"), f"tkb_scaled_norm_add_{suf}")(
-        _ptr(x), _ptr(y), _ptr(bias), _ptr(weight), _ptr(scale), c_float(mult), c_float(eps), _ptr(h_out), c_int(rows),
-        c_int(H), _stream()), "scaled_norm_add")
+        _ptr(x), _ptr(y), c_int(n_slices), ctypes.c_longlong(rows * H), _ptr(bias), _ptr(weight), _ptr(scale), c_float(mult),
+        c_float(eps), _ptr(h_out), c_int(rows), c_int(H), _stream()), "scaled_norm_add")
+
+
+def linear_out_f32(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor | None) -> torch.Tensor:
+    """a[M, K] @ w[N, K]^T for a consumer that reads float32 and can add slices (``scaled_norm_add``): with few rows
+    and a matrix of up to 32 M values the K-split product's float32 slices [slices, M, N], else whole float32 rows
+    [M, N].  (Measured on B200 at 8 rows: 2,048 x 8,192 14.5 us against the library's 23.5 us; 4,096 x 4,096 11 against
+    12.5; 4,096 x 14,336 35 against 29, and its eight slices cost the consumer another 9 us.)"""
+    if w.numel() <= (32 << 20) and can_use_few_rows(a, w):
+        return linear_few_rows(a, w, status)
+    return linear(a, w, out_dtype=torch.float32)
 
 
 def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:

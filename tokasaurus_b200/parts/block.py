@@ -97,7 +97,8 @@ class OutputNormBlock(Part):
 
     ``mult`` is a number, ``scale1`` / ``scale2`` optional per-channel vectors (a layer scale; tensor names).  The
     norms are RMS norms (``parts.norm.RMSNorm``: weight and eps).  The stream stays float32; the kernel that adds a
-    sublayer's normed output also writes the new stream in the activation type for the sublayer that reads it next.
+    sublayer's normed output also writes the new stream in the activation type for the sublayer that reads it next; a
+    sublayer's output may be the float32 slices of a K-split product (few rows), which that kernel adds.
     A mixer may carry an ``out_bias`` (the bias of its output projection), which is added before the norm."""
 
     def __init__(self, mixer: Mixer, mixer_norm, ffn: FeedForward | None, ffn_norm, mult: float = 1.0,

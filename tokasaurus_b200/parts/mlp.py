@@ -95,7 +95,7 @@ class ClampedGLU(FeedForward):
             gu = ops.linear(h, self.w_gate_up)
             act = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
             ops.clamped_glu(gu, act, self.limit, self.alpha, self.interleave)
-        return ops.linear(act, self.w_down, out_dtype=torch.float32)
+        return ops.linear_out_f32(act, self.w_down, ctx.status if ctx is not None else None)
 
 
 class PolyNormMLP(FeedForward):

@@ -120,7 +120,7 @@ class DecayedLinearAttention(Mixer):
             raw, g = _rows(raw, out_rows), _rows(g.contiguous(), out_rows)
         o = torch.empty(raw.shape, dtype=h.dtype, device=h.device)
         ops.gated_group_norm(raw, g, self.norm_w, o, 1, self.norm_eps, gate_first=False)
-        return ops.linear(o, self.w_o, out_dtype=torch.float32)
+        return ops.linear_out_f32(o, self.w_o, ctx.status)
 
 
 def _rows(t: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:

@@ -92,9 +92,9 @@ class SinkAttention(Mixer):
                 cut = torch.empty((out_rows.numel(), H * e), dtype=h.dtype, device=h.device)
                 ops.gather_rows(attn, out_rows, cut)
                 attn = cut
-            return ops.linear(attn, self.w_o, out_dtype=torch.float32)
+            return ops.linear_out_f32(attn, self.w_o, ctx.status)
         n_rows = T if out_rows is None else out_rows.numel()
         attn = torch.empty((n_rows, H * e), dtype=h.dtype, device=h.device)
         ops.attn_sink(q, attn, cache.k, ctx.token_seq, ctx.positions, tables.indptr, tables.page_ids, out_rows, n_rows,
                       self.sinks, H, G, d, e, cache.page_size, self.scale, self.softcap, self.window, ctx.status)
-        return ops.linear(attn, self.w_o, out_dtype=torch.float32)
+        return ops.linear_out_f32(attn, self.w_o, ctx.status)

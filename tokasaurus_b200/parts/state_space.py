@@ -85,4 +85,4 @@ class SelectiveStateSpace(Mixer):
             raw, z = _rows(raw, out_rows), _rows(z.contiguous(), out_rows)
         o = torch.empty(raw.shape, dtype=h.dtype, device=h.device)
         ops.gated_group_norm(raw, z, self.norm_w, o, self.norm_groups, self.norm_eps, gate_first=True)
-        return ops.linear(o, self.w_o, out_dtype=torch.float32)
+        return ops.linear_out_f32(o, self.w_o, ctx.status)
