@@ -411,7 +411,19 @@ B0, B1, B2 = dict(ssm(3, 20, 48, 1, 1, 5), mlp=ff(80, 1.0)), dict(lin(2, 40, 12,
 C0, C1, C2 = dict(lin(5, 8, 24, [0.999, 0.9, 0.8, 0.6, 0.3]), mlp=ff(96, 1.0)), dict(att(8, 1, 32, 16, 16, 0.18, 3.0), mlp=ff(64, 1.0)), \
     dict(ssm(6, 16, 16, 3, 2, 2), mlp=ff(40, 3.0))
 
+D0, D1 = dict(lin(2, 24, 24, [0.9, 0.97]), mlp=ff(64, 1.0)), dict(ssm(2, 40, 24, 2, 1, 4), mlp=ff(32, 1.2))
+E0, E1, E2 = dict(att(4, 2, 16, 16, 40, 0.3, 10.0), mlp=ff(48, 1.0)), dict(att(2, 2, 32, 8, 9, 0.2, 25.0), mlp=None), \
+    dict(att(3, 1, 16, 32, 70, 0.25, 15.0), mlp=ff(40, 1.0))
+
 MODELS = {
+    # no attention at all: no pages, only slots
+    "d": dict(page=16, lengths=[90, 20, 47, 3, 61],
+              config=dict(architecture="Daborax", vocab=89, width=80, norm=dict(eps=1e-6), embedding=dict(scale=4.0),
+                          residual_mult=0.8, layers=[D0, D1, shared(D0, 0)])),
+    # only attention, of three shapes and windows: three cache groups, no slots' state
+    "e": dict(page=8, lengths=[120, 33, 75, 9, 50],
+              config=dict(architecture="Daborax", vocab=101, width=64, norm=dict(eps=1e-5), embedding=dict(scale=2.0),
+                          residual_mult=0.9, layers=[E0, E1, E2, shared(E1, 1)])),
     # attention first with a window that is no multiple of the page size, a layer without a feed-forward, both kinds
     # of state, two layers that run with earlier layers' tensors
     "a": dict(page=8, lengths=[100, 37, 64, 5, 81, 1, 50],
@@ -525,12 +537,13 @@ def test_cuttings_match_plain(models, which, cut, dtype):
         cache.check()
         for rid, rc in cache.requests.items():
             slots.setdefault(rc.slot, set()).add(rid)
-            for p in rc.live_pages(0):
-                owners.setdefault(p, set()).add(rid)
+            for gi in range(len(cache.groups)):
+                for p in rc.live_pages(gi):
+                    owners.setdefault((gi, p), set()).add(rid)
     assert not cache.requests and cache.num_free_pages() == [g.allocator.num_pages for g in cache.groups]
     check_logits(cuttings.collect(steps, outs), m, dtype, cut)
     if cut == "mixed":
-        assert any(len(v) > 1 for v in owners.values()), "no page was used by two requests"
+        assert not cache.groups or any(len(v) > 1 for v in owners.values()), "no page was used by two requests"
         assert any(len(v) > 1 for v in slots.values()), "no slot was used by two requests"
 
 
@@ -590,7 +603,7 @@ def test_long_decoding_past_the_windows(models, dtype):
     back behind it, and the states are carried 150 steps."""
     from tokasaurus_b200.engine.trace import TraceReplayer
 
-    for which in ("a", "c"):
+    for which in ("a", "c", "d", "e"):
         m = models[which]
         toks = cuttings.random_tokens(160, m["config"]["vocab"], 7)
         want = plain.forward(m["config"], m["weights"], toks).numpy()
@@ -608,13 +621,15 @@ def plain_greedy(m, prompt, n):
     return out
 
 
+@pytest.mark.parametrize("which", ["a", "d", "e"])
 @pytest.mark.parametrize("graphs", [False, True])
-def test_greedy_generation_through_the_entry_point(models, graphs):
+def test_greedy_generation_through_the_entry_point(models, graphs, which):
     """Greedy generation in float32 through ``Engine.generate``: the scheduler admits, cuts prompts into portions,
-    decodes (from CUDA graphs or kernel by kernel) and frees; five requests in three slots, so slots are handed on."""
+    decodes (from CUDA graphs or kernel by kernel) and frees; five requests in three slots, so slots are handed on.
+    Also for a model without any pages and for one without any state."""
     from tokasaurus_b200.engine.engine import Engine
 
-    m = models["a"]
+    m = models[which]
     V = m["config"]["vocab"]
     prompts = [cuttings.random_tokens(n, V, 300 + n) for n in (30, 3, 41, 17, 9)]
     n_new = 10
