@@ -31,8 +31,10 @@ class TraceReplayer:
     def __init__(self, model_dir: str, dtype: str, max_tokens: int, page_size: int = 16, device: str = "cuda:0",
                  max_requests: int = 64):
         pool = ((max_tokens + page_size - 1) // page_size) * page_size
+        # a trace may bring a whole prompt in one step: no pool (a windowed group's neither) is smaller than the trace's tokens
         cfg = EngineConfig(model=model_dir, dtype=dtype, page_size=page_size, kv_cache_num_tokens=max(pool, page_size),
-                           max_seqs_per_forward=max_requests, device=device, use_cudagraphs=False)
+                           max_seqs_per_forward=max_requests, max_tokens_per_forward=max(8192, pool), device=device,
+                           use_cudagraphs=False)
         self.runner = ModelRunner(cfg)
         self.lengths: dict[str, int] = {}
 
