@@ -286,16 +286,28 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// cap * tanh(s / cap) in units of log2: tanh(x) = 1 - 2 / (e^(2x) + 1) with the exponential of a bounded argument.
-// The exponential and the quotient are each good to about 1e-7 of a result near 1, so the capped score is off by about
-// cap * 1e-7: the size of a float32 rounding of a score of the cap's own size (the FP32-pipe kernel calls tanhf).
-__device__ __forceinline__ float capped_log2(float s, float softcap, float inv_cap) {
-  if (softcap > 0.f) {
-    const float x = fminf(fmaxf(s * inv_cap, -15.f), 15.f);
-    const float e = ex2(2.f * LOG2E * x);
-    s = fmaf(-softcap, __fdividef(2.f, e + 1.f), softcap);
-  }
-  return s * LOG2E;
+// cap * tanh(scale * d / cap) in units of log2 from the raw dot product d: tanh(x) = 1 - 2 / (e^(2x) + 1), five
+// instructions a score.  k1 = 2 log2(e) scale / cap, so that e^(2x) = 2^(k1 d); an exponential that overflows gives
+// tanh = 1, one that underflows tanh = -1, as they should.  The exponential and the reciprocal are each good to about
+// 1e-7 of a result near 1, so the capped score is off by about cap * 1e-7: the size of a float32 rounding of a score of
+// the cap's own size (the FP32-pipe kernel calls tanhf).  Without a cap: d * scale * log2(e).
+struct ScoreMap {
+  float k1, c0, c1;  // capped: fma(rcp(ex2(k1 d) + 1), c1, c0) with c0 = cap log2(e), c1 = -2 c0;  plain: d * k1
+  bool capped;
+};
+__device__ __forceinline__ ScoreMap score_map(float scale, float softcap) {
+  ScoreMap m;
+  m.capped = softcap > 0.f;
+  m.k1 = m.capped ? 2.f * LOG2E * scale / softcap : scale * LOG2E;
+  m.c0 = softcap * LOG2E;
+  m.c1 = -2.f * m.c0;
+  return m;
+}
+__device__ __forceinline__ float mapped_score(float d, const ScoreMap& m) {
+  if (!m.capped) return d * m.k1;
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(ex2(d * m.k1) + 1.f));
+  return fmaf(r, m.c1, m.c0);
 }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -322,10 +334,11 @@ __device__ __forceinline__ void stage_tile(bf16* buf, const bf16* __restrict__ c
 
 // One warp, 16 rows, NT groups of 8 keys that start at row `kr0` of the staged tile (key index key0): scores, running
 // softmax, and the weighted sum of values.  lim_lo / lim_hi: the keys each of the thread's two rows may see.
-template <int NT>
+// MASKED false: every key of the span is seen by every row (the caller has checked), no limit is looked at.
+template <int NT, bool MASKED>
 __device__ __forceinline__ void attend(const bf16* buf, int kr0, int key0, const uint32_t (&qf)[KSTEPS][4], float (&o)[VT][4],
                                        float (&m)[2], float (&l)[2], const int (&lim_lo)[2], const int (&lim_hi)[2],
-                                       float scale, float softcap, float inv_cap, int lane) {
+                                       const ScoreMap& sm, int lane) {
   const int g = lane >> 2, t = lane & 3;
   float sc[NT][4];
 #pragma unroll
@@ -359,9 +372,11 @@ __device__ __forceinline__ void attend(const bf16* buf, int kr0, int key0, const
     for (int nt = 0; nt < NT; nt++)
 #pragma unroll
       for (int e = 0; e < 2; e++) {
-        const int key = key0 + nt * 8 + 2 * t + e;
-        float v = capped_log2(sc[nt][h * 2 + e] * scale, softcap, inv_cap);
-        if (key < lim_lo[h] || key > lim_hi[h]) v = -INFINITY;
+        float v = mapped_score(sc[nt][h * 2 + e], sm);
+        if (MASKED) {
+          const int key = key0 + nt * 8 + 2 * t + e;
+          if (key < lim_lo[h] || key > lim_hi[h]) v = -INFINITY;
+        }
         sc[nt][h * 2 + e] = v;
         mx = fmaxf(mx, v);
       }
@@ -432,7 +447,7 @@ attn_sink_tiles_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const
   const int r0 = tile * KT;              // first query of the tile within the portion
   const int rows = min(KT, n_q - r0);
   const int* table = page_ids + page_indptr[s];
-  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+  const ScoreMap sm = score_map(scale, softcap);
 
   uint32_t qf[KSTEPS][4];
   int lim_lo[2], lim_hi[2];
@@ -464,6 +479,7 @@ attn_sink_tiles_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const
   const int w_first = pos0 + r0 + warp * 16;
   const int w_lo = (window > 0 && w_first - window + 1 > 0) ? w_first - window + 1 : 0;
   const int w_hi = min(p_last, w_first + 15);
+  const int w_last_lo = (window > 0 && w_first + 15 - window + 1 > 0) ? w_first + 15 - window + 1 : 0;  // the last row's
   bool bad = false;
   stage_tile(bufs, cache, table, k_lo, k_lo, p_last, kvh, nkv, ps, num_pages, bad, tid);
   cp_async_commit();
@@ -479,8 +495,13 @@ attn_sink_tiles_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const
     }
     __syncthreads();
     const int key0 = k_lo + it * KT;
-    if (warp * 16 < rows && key0 <= w_hi && key0 + KT - 1 >= w_lo)  // warp-uniform: some row of the warp sees some key
-      attend<8>(cur, 0, key0, qf, o, m, l, lim_lo, lim_hi, scale, softcap, inv_cap, lane);
+    if (warp * 16 < rows && key0 <= w_hi && key0 + KT - 1 >= w_lo) {  // warp-uniform: some row of the warp sees some key
+      // all 16 rows live and the whole tile inside every row's window and before the warp's first query: no masks
+      if (warp * 16 + 16 <= rows && key0 + KT - 1 <= w_first && key0 >= w_last_lo)
+        attend<8, false>(cur, 0, key0, qf, o, m, l, lim_lo, lim_hi, sm, lane);
+      else
+        attend<8, true>(cur, 0, key0, qf, o, m, l, lim_lo, lim_hi, sm, lane);
+    }
     __syncthreads();  // the buffer is free for the tile after next
   }
   report_bad_page(bad, status);
@@ -522,7 +543,7 @@ attn_sink_single_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
   const int tok = seq_q_start[s];
   const int p = seq_kv_len[s] - 1;
   const int* table = page_ids + page_indptr[s];
-  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+  const ScoreMap sm = score_map(scale, softcap);
   const int k_lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
 
   uint32_t qf[KSTEPS][4];
@@ -566,7 +587,7 @@ attn_sink_single_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
     }
     __syncthreads();
     const int key0 = k_lo + (it0 + it) * KT + warp * 16;
-    if (key0 <= p) attend<2>(cur, warp * 16, key0, qf, o, m, l, lim_lo, lim_hi, scale, softcap, inv_cap, lane);
+    if (key0 <= p) attend<2, true>(cur, warp * 16, key0, qf, o, m, l, lim_lo, lim_hi, sm, lane);
     __syncthreads();
   }
   cp_async_wait<0>();
